@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and model builder.
 
-A model folder's ``config.json`` names its architecture in ``architectures[0]`` and/or
-``model_type``; ``resolve`` looks both up here (the reference dispatches on ``model_type`` with a
+A model folder's ``config.json`` names its architecture in ``architectures[0]``, ``architecture``
+and/or ``model_type``; ``resolve`` looks both up here (the reference dispatches on ``model_type`` with a
 most-specific-first prefix chain, src/quanta/shim/omlx.py:307-341, and raises on an unknown one).
 
 Adding an architecture is one call to ``register_architecture`` from the module that defines its
@@ -47,6 +47,8 @@ def resolve(raw_config: dict) -> Architecture:
     """Architecture for a raw ``config.json`` dictionary; unknown names raise with the known list."""
     _load_builtin()
     candidates = list(raw_config.get("architectures") or [])
+    if raw_config.get("architecture"):
+        candidates.append(str(raw_config["architecture"]))
     if raw_config.get("model_type"):
         candidates.append(str(raw_config["model_type"]))
     tc = raw_config.get("text_config") or {}
@@ -71,4 +73,18 @@ def load_config(model_dir) -> tuple[Architecture, Any]:
     if gp.exists():
         gen = json.loads(gp.read_text())
     arch = resolve(raw)
-    return arch, arch.config_cls.from_dict(raw, generation=gen)
+    cfg = arch.config_cls.from_dict(raw, generation=gen)
+    if hasattr(cfg, "with_tensor_shapes"):
+        # sizes that are no keys of config.json are the checkpoint's tensor shapes
+        from ..weights.safetensors_io import CheckpointFolder
+        try:
+            ckpt = CheckpointFolder(d)
+        except (FileNotFoundError, OSError):
+            ckpt = None
+        if ckpt is not None:
+            try:
+                names = set(ckpt.names())
+                cfg = cfg.with_tensor_shapes(lambda n: tuple(ckpt.meta(n)[1]) if n in names else None)
+            finally:
+                ckpt.close()
+    return arch, cfg

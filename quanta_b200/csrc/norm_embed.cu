@@ -7,11 +7,11 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// h[t,:] = float(table[ids[t],:])     (reference: src/quanta/minimax/model.py:91)
+// h[t,:] = float(table[ids[t],:]) * scale     (reference: src/quanta/minimax/model.py:91)
 // ---------------------------------------------------------------------------------------------
 template <typename W>
 __global__ void embedding_kernel(float* __restrict__ h, const W* __restrict__ table,
-                                 const int* __restrict__ ids, int T, int H, int V, int* status) {
+                                 const int* __restrict__ ids, int T, int H, int V, float scale, int* status) {
   const int t = blockIdx.x;
   if (t >= T) return;
   const int id = ids[t];
@@ -26,18 +26,20 @@ __global__ void embedding_kernel(float* __restrict__ h, const W* __restrict__ ta
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       float v[8];
       QbVec8<W>::load(row + i, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= scale;
       QbVec8<float>::store(out + i, v);
     }
   } else {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = qb_to_float<W>(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = qb_to_float<W>(row[i]) * scale;
   }
 }
 
 extern "C" int qb_embedding(float* h, const void* table, int table_dtype, const int* ids, int T, int H,
-                            int V, int* status, cudaStream_t stream) {
+                            int V, float scale, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   QB_DISPATCH_DTYPE(table_dtype, W,
-                    embedding_kernel<W><<<T, 256, 0, stream>>>(h, (const W*)table, ids, T, H, V, status));
+                    embedding_kernel<W><<<T, 256, 0, stream>>>(h, (const W*)table, ids, T, H, V, scale, status));
   QB_LAUNCH_CHECK();
   return 0;
 }

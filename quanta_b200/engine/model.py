@@ -12,7 +12,7 @@ from pathlib import Path
 
 import torch
 
-from .. import matmul
+from .. import kernels, matmul
 from ..config.registry import load_config
 from ..parts import block as _block  # noqa: F401  (registers the built-in block, embedding and head)
 from ..parts.base import CacheSpec, Part, TensorSpec, make
@@ -47,6 +47,9 @@ class Model:
         self.head = make("head", spec.head)
         self.schedule = list(spec.schedule)
         self.loaded = False
+        # a list to have ``forward`` append the residual stream after every schedule entry (float32 [T, hidden]
+        # copies; costs a kernel and memory per entry, and keeps steps out of captured graphs' fast path)
+        self.residual_trace: list | None = None
 
     # ---- weights -------------------------------------------------------------------------------
     def parts(self):
@@ -95,16 +98,28 @@ class Model:
                 for e in self.schedule]
 
     def state_needs(self) -> list[dict]:
-        return [self.blocks[e.layer].mixer.state_spec() for e in self.schedule]
+        return [self.blocks[e.layer].state_spec() for e in self.schedule]
 
     # ---- one step --------------------------------------------------------------------------------
     def forward(self, token_ids, ctx, caches, states, want_rows):
         """``token_ids`` int32 [T]; ``caches[pos]``/``states[pos]`` per schedule position; ``want_rows``
         int32 rows whose logits are returned ([n, vocab] float32) or None."""
         h = self.embedding.forward(token_ids, ctx)
+        embedded = h.clone() if any(e.add_embedding for e in self.schedule) else None
         pending = None
         for pos, entry in enumerate(self.schedule):
+            if entry.add_embedding:
+                # the stream so far, then the embedded tokens once more, both summed in float32
+                if pending is not None:
+                    kernels.residual_add(h, pending)
+                    pending = None
+                kernels.residual_add(h, embedded)
             pending = self.blocks[entry.layer].forward(h, pending, ctx, caches[pos], states[pos])
+            if self.residual_trace is not None:
+                now = h.clone()
+                if pending is not None:
+                    kernels.residual_add(now, pending)
+                self.residual_trace.append(now)
         if want_rows is None or want_rows.numel() == 0:
             return None
         return self.head.forward(h, pending, want_rows, ctx)

@@ -68,7 +68,7 @@ class Engine:
         self.device = model.device
         if self.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
-        kernels.lib()                       # build/load the kernels now; fails loudly if that is impossible
+        kernels.lib("core")                 # build/load the common kernels now; fails loudly if that is impossible
         self.page_size = int(page_size)
         needs = model.cache_needs()
         self.manager = CacheManager(needs, page_size, num_pages, max_requests)

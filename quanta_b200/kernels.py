@@ -31,8 +31,10 @@ class KernelError(RuntimeError):
     pass
 
 
-def lib() -> ctypes.CDLL:
-    return _build.load()
+def lib(unit: str | None = None):
+    """The kernel library (entry points as attributes; a unit of kernels is compiled and loaded at the first
+    call into it).  ``unit``: build and load that unit now."""
+    return _build.load(unit)
 
 
 def _code(t: torch.Tensor) -> int:
@@ -95,14 +97,16 @@ def raise_on_status(status_host) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-def embedding(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> None:
+def embedding(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """``h[t] = float32(table[ids[t]]) * scale``."""
     _want(h, torch.float32, "h"); _want(ids, torch.int32, "ids")
     T, H = h.shape
     V = table.shape[0]
     if table.shape[1] != H or ids.numel() != T:
         raise ValueError("embedding: shape mismatch")
-    _check(lib().qb_embedding(_p(h), _p(table), _code(table), _p(ids), T, H, V, _p(status), _stream()),
-           "embedding")
+    _check(lib().qb_embedding(_p(h), _p(table), _code(table), _p(ids), T, H, V, ctypes.c_float(scale), _p(status),
+                              _stream()), "embedding")
 
 
 def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -129,6 +133,17 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     _check(lib().qb_add_rmsnorm(_p(h), _p(delta), _code(delta) if delta is not None else F32, S, _p(weight),
                                 _p(out), _code(out) if out is not None else F32, _p(rows), n, H,
                                 ctypes.c_float(eps), int(store_h), _stream()), "add_rmsnorm")
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    """``h += sum_s delta[:, s]`` in float32 (``delta`` ``[T, H]`` or ``[T, S, H]``), without a norm."""
+    _want(h, torch.float32, "h")
+    T, H = h.shape
+    S = delta.shape[1] if delta.dim() == 3 else 1
+    if delta.shape[0] != T or delta.shape[-1] != H:
+        raise ValueError("residual_add: delta shape mismatch")
+    _check(lib().qb_add_rmsnorm(_p(h), _p(delta), _code(delta), S, ctypes.c_void_p(0), ctypes.c_void_p(0), F32,
+                                ctypes.c_void_p(0), T, H, ctypes.c_float(0.0), 1, _stream()), "residual_add")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -464,3 +479,113 @@ def apply_penalties(logits, prev, prev_off, pparams) -> None:
     n, V = logits.shape
     _check(lib().qb_apply_penalties(_p(logits), n, V, _p(prev), _p(prev_off), _p(pparams), _stream()),
            "apply_penalties")
+
+
+# ---- short convolution, delta-rule recurrence, latent attention ---------------------------------------
+def short_conv(x, weight, state, out, tok_req, req_start, req_slot) -> None:
+    """``out[t] = x[t] + sum_j weight[:, j] * x[t - taps + 1 + j]`` over each request's own rows, the rows
+    before a portion taken from ``state`` ``[slots, taps - 1, C]`` (float32, newest last), which then holds
+    the request's last ``taps - 1`` inputs.  ``x`` float32 ``[T, C]``, ``weight`` float32 ``[C, taps]``."""
+    _want(x, torch.float32, "x"); _want(weight, torch.float32, "weight"); _want(state, torch.float32, "state")
+    T, C = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != C or tuple(out.shape) != (T, C) or tuple(state.shape[1:]) != (max(taps - 1, 0), C):
+        raise ValueError("short_conv: shape mismatch")
+    R = req_slot.numel()
+    _check(lib().qb_short_conv(_p(x), _p(weight), _p(state), _p(out), _code(out), _p(tok_req), _p(req_start),
+                               _p(req_slot), T, R, C, taps, _stream()), "short_conv", 2 if taps > 1 else 1)
+
+
+DELTA_RULE_MAX_DIM = 256
+
+
+def delta_rule(proj, offsets, wpre, a_bias, w_bias, state, out, req_start, req_slot, n_heads: int, dim: int,
+               decay_scale: float, unit_eps: float) -> None:
+    """The recurrence ``S <- diag(w) S - (a u)(u^T S) + k v^T``, ``o = S^T r`` per (request, head) over the
+    step's tokens, from and into ``state`` ``[slots, heads, dim, dim]`` float32.  ``proj`` float32 ``[T, P]``
+    holds r, k, v and the pre-activation of a at the column ``offsets`` (r, k, v, a), heads x dim each;
+    ``wpre`` float32 ``[T, heads*dim]`` the pre-activation of the decay; ``out`` float32 ``[T, heads, dim]``."""
+    for t, n in ((proj, "proj"), (wpre, "wpre"), (a_bias, "a_bias"), (w_bias, "w_bias"), (state, "state"), (out, "out")):
+        _want(t, torch.float32, n)
+    T = proj.shape[0]
+    HD = n_heads * dim
+    if (tuple(wpre.shape) != (T, HD) or out.numel() != T * HD or a_bias.numel() != HD or w_bias.numel() != HD
+            or tuple(state.shape[1:]) != (n_heads, dim, dim) or any(o < 0 or o + HD > proj.shape[1] for o in offsets)):
+        raise ValueError("delta_rule: shape mismatch")
+    if proj.stride(1) != 1:
+        raise ValueError("delta_rule: proj rows must be dense")
+    r_off, k_off, v_off, a_off = (int(o) for o in offsets)
+    R = req_slot.numel()
+    _check(lib().qb_delta_rule(ctypes.c_void_p(proj.data_ptr()), int(proj.stride(0)), r_off, k_off, v_off, a_off,
+                               _p(wpre), _p(a_bias), _p(w_bias), _p(state), _p(out), _p(req_start), _p(req_slot),
+                               R, T, n_heads, dim, ctypes.c_float(decay_scale), ctypes.c_float(unit_eps), _stream()),
+           "delta_rule")
+
+
+def head_norm_gate(o, proj, gate_off: int, gain, out, n_heads: int, dim: int, eps: float) -> None:
+    """``out[t, h] = o[t, h] / rms(o[t, h]) * gain[h] * sigmoid(proj[t, gate_off + h*dim ...])``."""
+    _want(o, torch.float32, "o"); _want(proj, torch.float32, "proj"); _want(gain, torch.float32, "gain")
+    T = proj.shape[0]
+    if o.numel() != T * n_heads * dim or tuple(out.shape) != (T, n_heads * dim) or gain.numel() != n_heads * dim:
+        raise ValueError("head_norm_gate: shape mismatch")
+    gate = ctypes.c_void_p(proj.data_ptr() + 4 * int(gate_off))
+    _check(lib().qb_head_norm_gate(_p(o), gate, int(proj.stride(0)), _p(gain), _p(out), _code(out), T, n_heads, dim,
+                                   ctypes.c_float(eps), _stream()), "head_norm_gate")
+
+
+def tanh_cols(x, off: int, n: int, out) -> None:
+    """``out[t, :n] = tanh(x[t, off : off + n])`` in the dtype of ``out``."""
+    _want(x, torch.float32, "x")
+    T = x.shape[0]
+    if tuple(out.shape) != (T, n) or off + n > x.shape[1]:
+        raise ValueError("tanh_cols: shape mismatch")
+    _check(lib().qb_tanh_cols(ctypes.c_void_p(x.data_ptr()), int(x.stride(0)), int(off), _p(out), _code(out), T, n,
+                              _stream()), "tanh_cols")
+
+
+LATENT_MAX_RANK = 512
+
+
+def latent_write(dkv, gain, inv_freq, cache, tok_pos, tok_req, block_table, rank: int, rot: int, rotated: int,
+                 page_size: int, eps: float, status) -> None:
+    """Rows ``[T, rank + rot]`` float32 -> the cache rows of their positions: RMS norm with ``gain`` of the
+    first ``rank``, rotation by the position of the first ``rotated`` of the last ``rot``.  ``cache`` ``[pages, 1, page_size, rank + rot]``."""
+    _want(dkv, torch.float32, "dkv"); _want(gain, torch.float32, "gain"); _want(inv_freq, torch.float32, "inv_freq")
+    T = dkv.shape[0]
+    if (dkv.shape[1] != rank + rot or gain.numel() != rank or inv_freq.numel() != rotated // 2
+            or tuple(cache.shape[1:]) != (1, page_size, rank + rot)):
+        raise ValueError("latent_write: shape mismatch")
+    _check(lib().qb_latent_write(_p(dkv), _p(gain), _p(inv_freq), _p(cache), _code(cache), _p(tok_pos), _p(tok_req),
+                                 _p(block_table), block_table.shape[1], T, rank, rot, int(rotated), page_size,
+                                 cache.shape[0], ctypes.c_float(eps), _p(status), _stream()), "latent_write")
+
+
+def latent_query(q, inv_freq, q_plain, q_rot, tok_pos, n_heads: int, dim: int, rot: int, rotated: int) -> None:
+    """``q`` float32 ``[T, heads, dim + rot]`` -> ``q_plain`` ``[heads, T, dim]`` and ``q_rot`` float32
+    ``[T, heads, rot]``, its first ``rotated`` dimensions rotated by the position."""
+    _want(q, torch.float32, "q"); _want(q_rot, torch.float32, "q_rot")
+    T = q.shape[0]
+    if q.numel() != T * n_heads * (dim + rot) or q_plain.numel() != T * n_heads * dim or q_rot.numel() != T * n_heads * rot:
+        raise ValueError("latent_query: shape mismatch")
+    _check(lib().qb_latent_query(_p(q), _p(inv_freq), _p(q_plain), _code(q_plain), _p(q_rot), _p(tok_pos), T, n_heads,
+                                 dim, rot, int(rotated), _stream()), "latent_query")
+
+
+def latent_attend(q_lat, q_rot, cache, sink, out, tok_pos, tok_req, block_table, scale: float, n_ranges: int,
+                  status) -> None:
+    """Causal softmax attention of every token and head over the cached latent rows, with an optional sink.
+    ``q_lat`` ``[heads, T, rank]``, ``q_rot`` float32 ``[T, heads, rot]``, ``out`` ``[heads, T, rank]``; each
+    token's keys are cut into ``n_ranges`` ranges that run as blocks of their own and are merged in order."""
+    H, T, C = q_lat.shape
+    num_pages, one, page_size, W = cache.shape
+    R = W - C
+    if one != 1 or q_rot.numel() != T * H * R or tuple(out.shape) != (H, T, C) or out.dtype != cache.dtype:
+        raise ValueError("latent_attend: shape/dtype mismatch")
+    if sink is not None:
+        _want(sink, torch.float32, "sink")
+    part = torch.empty(T * H * n_ranges * (C + 2), dtype=torch.float32, device=q_lat.device)
+    _check(lib().qb_latent_attend(_p(q_lat), _code(q_lat), _p(q_rot), _p(cache), _code(cache), _p(part), _p(tok_pos),
+                                  _p(tok_req), _p(block_table), block_table.shape[1], T, H, C, R, page_size, num_pages,
+                                  int(n_ranges), ctypes.c_float(scale), _p(status), _stream()), "latent_attend")
+    _check(lib().qb_latent_merge(_p(part), _p(sink), _p(out), _code(out), T, H, C, int(n_ranges), _stream()),
+           "latent_merge")

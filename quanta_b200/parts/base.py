@@ -1,9 +1,10 @@
 """What a part is, and the registries parts are chosen from.
 
-A model is put together from parts of seven kinds: ``mixer`` (attention here), ``feed_forward``
-(dense or routed experts), ``norm``, ``position`` (position encoding), ``block`` (how a layer
-arranges the other four), ``embedding`` (token ids to the residual stream) and ``head`` (the residual
-stream to logits).  A part takes every size and constant as a constructor parameter, names
+A model is put together from parts of eight kinds: ``mixer`` (attention, or a recurrence with a state
+of fixed size), ``feed_forward`` (dense or routed experts), ``norm``, ``position`` (position encoding),
+``time_conv`` (a short convolution over time in front of a sublayer), ``block`` (how a layer arranges
+the others), ``embedding`` (token ids to the residual stream) and ``head`` (the residual stream to
+logits).  A part takes every size and constant as a constructor parameter, names
 the checkpoint tensors it needs (``tensor_specs``), receives them (``load``) and runs on the tokens
 of one step (``forward``).  No part knows which model it is in; an architecture is a function from
 its configuration to a ``ModelSpec`` that names parts and parameters layer by layer.
@@ -19,7 +20,7 @@ from typing import Any, Callable
 
 import torch
 
-KINDS = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+KINDS = ("mixer", "feed_forward", "norm", "position", "time_conv", "block", "embedding", "head")
 _REGISTRY: dict[str, dict[str, type]] = {k: {} for k in KINDS}
 
 
@@ -224,6 +225,18 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TimeConv(Part):
+    """A short causal convolution over a request's rows.  Its last inputs are per-request state:
+    ``state_spec`` names them like a mixer's, and ``forward(x float32 [T, C], ctx, state, out)`` reads and
+    updates the rows ``ctx.req_slot`` of ``state[name]``."""
+
+    def state_spec(self) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
+        return {}
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, state: dict[str, torch.Tensor], out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
 class Embedding(Part):
     """Token ids to the float32 residual stream: ``forward(ids int32 [T], ctx) -> [T, hidden]``."""
 
@@ -243,6 +256,10 @@ class Block(Part):
     """Arrangement of norm, mixer and feed-forward in one layer.  ``forward`` takes the residual stream
     ``h`` (float32) and the not-yet-added contribution of the layer before, and returns the new pending
     contribution; every addition to ``h`` happens inside a norm kernel."""
+
+    def state_spec(self) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
+        """Per-request state of the whole layer: the mixer's, plus what the block's other parts keep."""
+        return self.mixer.state_spec()
 
     def forward(self, h, pending, ctx, cache, state):
         raise NotImplementedError

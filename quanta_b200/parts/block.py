@@ -37,14 +37,76 @@ class PreNormBlock(Block):
         return self.feed_forward.forward(x2, ctx)
 
 
-@register("embedding", "token_table")
-class TokenTable(Embedding):
-    """``h = table[ids]`` into the float32 residual stream (src/quanta/minimax/model.py:91)."""
+@register("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and a norm after each sublayer: ``h += post_1(mixer(conv(pre_1(h))))`` and, where the
+    layer has a feed-forward, ``h += post_2(feed_forward(pre_2(h)))``.  ``conv`` (optional) is a short
+    convolution over time on the mixer's input; its last inputs are part of the layer's per-request state.
+    Both sums are float32 and happen inside the next pre-norm (or the head's norm); the post-norms write
+    float32, so a sublayer's contribution is never rounded to the activation dtype."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str):
-        self.V, self.H, self.weight_name = int(vocab_size), int(hidden_size), weight_name
+    def __init__(self, hidden_size: int, mixer, mixer_norm, mixer_post_norm, feed_forward=None,
+                 feed_forward_norm=None, feed_forward_post_norm=None, conv=None):
+        self.hidden = int(hidden_size)
+        self.mixer = make("mixer", mixer)
+        self.mixer_norm = make("norm", mixer_norm)
+        self.mixer_post_norm = make("norm", mixer_post_norm)
+        self.conv = make("time_conv", conv) if conv is not None else None
+        self.feed_forward = make("feed_forward", feed_forward) if feed_forward is not None else None
+        self.feed_forward_norm = self.feed_forward_post_norm = None
+        if self.feed_forward is not None:
+            self.feed_forward_norm = make("norm", feed_forward_norm)
+            self.feed_forward_post_norm = make("norm", feed_forward_post_norm)
+
+    def children(self):
+        parts = [self.mixer_norm, self.conv, self.mixer, self.mixer_post_norm, self.feed_forward_norm,
+                 self.feed_forward, self.feed_forward_post_norm]
+        return [p for p in parts if p is not None]
+
+    def state_spec(self):
+        spec = dict(self.mixer.state_spec())
+        if self.conv is not None:
+            for name, need in self.conv.state_spec().items():
+                if name in spec:
+                    raise ValueError(f"the mixer and the convolution both keep a state named {name!r}")
+                spec[name] = need
+        return spec
+
+    def _post(self, norm, y):
+        if y.dtype != torch.float32:
+            y = y.float()
+        d = torch.empty(y.shape, dtype=torch.float32, device=y.device)
+        norm.forward(y, None, d)
+        return d
+
+    def forward(self, h, pending, ctx, cache, state):
+        T = h.shape[0]
+        x = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
+        if self.conv is None:
+            self.mixer_norm.forward(h, pending, x)
+        else:
+            normed = torch.empty((T, self.hidden), dtype=torch.float32, device=h.device)
+            self.mixer_norm.forward(h, pending, normed)
+            self.conv.forward(normed, ctx, state, x)
+        d = self._post(self.mixer_post_norm, self.mixer.forward(x, ctx, cache, state))
+        if self.feed_forward is None:
+            return d
+        x2 = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
+        self.feed_forward_norm.forward(h, d, x2)
+        return self._post(self.feed_forward_post_norm, self.feed_forward.forward(x2, ctx))
+
+
+@register("embedding", "token_table")
+class TokenTable(Embedding):
+    """``h = table[ids] * scale`` into the float32 residual stream (src/quanta/minimax/model.py:91; the
+    reference has no scale)."""
+
+    graph_safe = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, scale: float = 1.0):
+        self.V, self.H, self.weight_name, self.scale = int(vocab_size), int(hidden_size), weight_name, float(scale)
         self.table = None
 
     def tensor_specs(self):
@@ -55,7 +117,7 @@ class TokenTable(Embedding):
 
     def forward(self, ids, ctx):
         h = torch.empty((ids.numel(), self.H), dtype=torch.float32, device=ids.device)
-        kernels.embedding(h, self.table, ids, ctx.status)
+        kernels.embedding(h, self.table, ids, ctx.status, self.scale)
         return h
 
 

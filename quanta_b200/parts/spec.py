@@ -2,7 +2,9 @@
 
 ``ModelSpec.layers`` are the layers that own weights; ``ModelSpec.schedule`` is the order in which
 they run, as data.  An entry may name a layer that already ran (its weights are reused, with a cache
-and state of its own), and may read the cache that an earlier entry wrote instead of writing one.
+and state of its own), may read the cache that an earlier entry wrote instead of writing one, and may
+have the embedding's output added to the residual stream before it runs (a range of layers that is
+walked several times, each later pass starting from the stream plus the embedded tokens).
 """
 
 from __future__ import annotations
@@ -14,6 +16,7 @@ from dataclasses import dataclass, field
 class ScheduleEntry:
     layer: int                         # index into ModelSpec.layers
     read_cache_of: int | None = None   # schedule position whose cache this entry reads (it writes none)
+    add_embedding: bool = False        # the embedding's output is added to the residual stream before this entry runs
 
 
 @dataclass
