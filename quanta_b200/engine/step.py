@@ -21,6 +21,7 @@ and it is zeroed when the request is freed.
 
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass
 
 import numpy as np
@@ -49,6 +50,7 @@ class _DecodeGraph:
         self.logits = None
         self.launches = 0
         self.used_at = 0          # the engine's step count when it last ran
+        self.failed = 0           # captures of this shape that did not succeed
 
 
 def _fill(host: torch.Tensor, pieces: list) -> None:
@@ -94,6 +96,7 @@ class Engine:
         self.max_graphs = max(1, int(max_graphs))
         self._graph_pool = None        # one memory pool for all captured steps: only one of them runs at a time
         self.graph_replays = 0
+        self.capture_failures = 0
         # one record per state slot (csrc/request_state.h).  Among other things it holds the token last
         # sampled for the request: a decode step can take its ids from there, so that it can be launched
         # before the host has read them
@@ -130,7 +133,7 @@ class Engine:
         graphs = [g for g in self._graphs.values() if g.graph is not None]
         held = sum(g.logits.numel() * g.logits.element_size() + g.dev.numel() * 4 for g in graphs)
         return {**self.manager.stats(), "graphs": len(graphs), "graph_output_bytes": held,
-                "graph_replays": self.graph_replays}
+                "graph_replays": self.graph_replays, "capture_failures": self.capture_failures}
 
     def check(self) -> None:
         """Read the device status words (synchronises) and raise if a kernel refused an index."""
@@ -296,7 +299,7 @@ class Engine:
         bucket = self._bucket(max_len_after)
         key = (B, bucket)
         g = self._graphs.setdefault(key, _DecodeGraph())
-        if g.graph is None and g.seen < 1:
+        if g.graph is None and (g.seen < 1 or g.failed >= 2):
             g.seen += 1
             return self._run(entries)            # first time at this shape: eager (also warms the libraries up)
         max_pages = -(-bucket // ps)
@@ -325,9 +328,22 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                kernels.slots_advance(self.slots, ctx.req_slot, ctx.req_start, ctx.req_len_after, B, self.status)
-                g.logits = self.model.forward(d_ids, ctx, caches, self.state, d_want)
+            try:
+                # relaxed: a kernel that is launched for the first time inside the capture (a library picks
+                # another kernel for the capture stream's workspace) may be loaded there, which allocates
+                with torch.cuda.graph(graph, pool=self._graph_pool, capture_error_mode="relaxed"):
+                    kernels.slots_advance(self.slots, ctx.req_slot, ctx.req_start, ctx.req_len_after, B, self.status)
+                    g.logits = self.model.forward(d_ids, ctx, caches, self.state, d_want)
+            except RuntimeError as e:
+                # nothing of a capture runs, so nothing has changed: the step runs kernel by kernel, and the
+                # shape is tried once more before it is left to run that way for good
+                kernels.LAUNCHES = before
+                g.logits, g.failed = None, g.failed + 1
+                self.capture_failures += 1
+                print(f"[quanta_b200] capturing the decode step {key} failed ({str(e).splitlines()[0]}); "
+                      f"it runs kernel by kernel", file=sys.stderr, flush=True)
+                torch.cuda.synchronize()
+                return self._run(entries)
             g.launches = kernels.LAUNCHES - before
             g.graph = graph
             self._drop_old_graphs(keep=key)

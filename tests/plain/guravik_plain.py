@@ -44,8 +44,11 @@ def causal_conv(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def rotate_half(x: torch.Tensor, pos: torch.Tensor, base: float) -> torch.Tensor:
-    """``x`` [T, ..., d] with d even: pair (i, i + d/2) turned by pos * base^(-2i/d)."""
+def rotate_half(x: torch.Tensor, pos: torch.Tensor, base: float, dims: int | None = None) -> torch.Tensor:
+    """``x`` [T, ..., n]: the first ``dims`` (default all; even) dimensions are rotated, pair (i, i + dims/2)
+    turned by pos * base^(-2i/dims); the rest pass unchanged."""
+    if dims is not None and dims < x.shape[-1]:
+        return torch.cat([rotate_half(x[..., :dims], pos, base), x[..., dims:]], -1) if dims else x
     d = x.shape[-1]
     half = d // 2
     freq = base ** (-2.0 * torch.arange(half, dtype=torch.float32, device=x.device) / d)
@@ -55,9 +58,31 @@ def rotate_half(x: torch.Tensor, pos: torch.Tensor, base: float) -> torch.Tensor
     return torch.cat([u * c - v * s, v * c + u * s], -1)
 
 
+def delta_recurrence(r, k, v, a, decay, S=None, unit_eps: float = 1e-6):
+    """``r, k, v, a, decay`` [T, H, D]; state S [H, D(key), D(value)] (zeros if None).  Per token:
+    S <- diag(decay) S - (a * u)(u^T S) + k v^T with both terms from the old S and u the unit key; o = S^T r.
+    Returns (o [T, H, D], S)."""
+    T, H, D = r.shape
+    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+    S = torch.zeros(H, D, D, dtype=torch.float32, device=r.device) if S is None else S.clone()
+    out = torch.zeros(T, H, D, dtype=torch.float32, device=r.device)
+    for t in range(T):
+        uS = torch.einsum("hk,hkv->hv", u[t], S)
+        S = decay[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hk,hkv->hv", r[t], S)
+    return out, S
+
+
+def sink_softmax(s: torch.Tensor, sink: torch.Tensor | None) -> torch.Tensor:
+    """Softmax over the last axis of ``s`` [H, T, J] whose denominator also holds exp(sink[h]) (no sink: plain)."""
+    if sink is None:
+        return torch.softmax(s, -1)
+    top = torch.maximum(s.max(-1).values, sink[:, None])
+    e = torch.exp(s - top[..., None])
+    return e / (e.sum(-1, keepdim=True) + torch.exp(sink[:, None] - top)[..., None])
+
+
 def delta_rule_mixer(h: torch.Tensor, W: dict, m: dict, eps: float) -> torch.Tensor:
-    """Recurrence per head with state S [dim_k, dim_v]:
-    S <- diag(w) S - (a * u)(u^T S) + k v^T (both terms from the old S), o = S^T r."""
     T = h.shape[0]
     H, D = m["heads"], m["dim"]
     r = (h @ W["r"].T).view(T, H, D)
@@ -66,13 +91,7 @@ def delta_rule_mixer(h: torch.Tensor, W: dict, m: dict, eps: float) -> torch.Ten
     g = torch.sigmoid(h @ W["g"].T)
     a = torch.sigmoid(h @ W["a"].T + W["a.b"]).view(T, H, D)
     decay = torch.exp(-math.exp(-0.5) * torch.sigmoid(torch.tanh(h @ W["w1"].T) @ W["w2"].T + W["w0"])).view(T, H, D)
-    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    S = torch.zeros(H, D, D, dtype=torch.float32, device=h.device)
-    out = torch.zeros(T, H, D, dtype=torch.float32, device=h.device)
-    for t in range(T):
-        uS = torch.einsum("hk,hkv->hv", u[t], S)
-        S = decay[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hk,hkv->hv", r[t], S)
+    out, _ = delta_recurrence(r, k, v, a, decay)
     out = rms(out, eps).reshape(T, H * D) * W["norm"] * g
     return out @ W["o"].T
 
@@ -83,17 +102,15 @@ def latent_attention_mixer(h: torch.Tensor, W: dict, m: dict, eps: float) -> tor
     pos = torch.arange(T, device=h.device)
     cq = rms_norm(h @ W["dq"].T, W["dq.norm"], eps)
     q = (cq @ W["uq"].T).view(T, H, D + R)
-    q_plain, q_rot = q[..., :D], rotate_half(q[..., D:], pos, m["rot"]["base"])
+    q_plain, q_rot = q[..., :D], rotate_half(q[..., D:], pos, m["rot"]["base"], m["rot"]["dims"])
     dkv = h @ W["dkv"].T
     c = rms_norm(dkv[:, :C], W["dkv.norm"], eps)
-    k_rot = rotate_half(dkv[:, C:], pos, m["rot"]["base"])                # [T, R], one for all heads
+    k_rot = rotate_half(dkv[:, C:], pos, m["rot"]["base"], m["rot"]["dims"])    # [T, R], one for all heads
     k_plain = (c @ W["uk"].T).view(T, H, D)
     val = (c @ W["uv"].T).view(T, H, V)
     s = (torch.einsum("thd,jhd->htj", q_plain, k_plain) + torch.einsum("thr,jr->htj", q_rot, k_rot)) * m["scale"]
     s = s.masked_fill(pos[None, None, :] > pos[None, :, None], float("-inf"))
-    top = torch.maximum(s.max(-1).values, W["sink"][:, None])
-    e = torch.exp(s - top[..., None])
-    p = e / (e.sum(-1, keepdim=True) + torch.exp(W["sink"][:, None] - top)[..., None])
+    p = sink_softmax(s, W.get("sink"))
     o = torch.einsum("htj,jhv->thv", p, val).reshape(T, H * V)
     return o @ W["o"].T
 
@@ -144,3 +161,74 @@ def forward(weights: dict, cfg: dict, tokens, with_layers: bool = False):
         after.append(x)
     logits = rms_norm(x, weights["final.norm"], cfg["norm"]["eps"]) @ weights["head"].T
     return (logits, torch.stack(after)) if with_layers else logits
+
+
+def tensor_shapes(cfg: dict, decay_rank: int = 16) -> dict:
+    """Name -> (shape, role) of every tensor of a model of this configuration; role is one of matrix, gain,
+    bias, conv, sink (for tests that draw their own weights)."""
+    W, out = cfg["width"], {}
+    out["embed"] = ((cfg["vocab"], W), "embed")
+    out["head"] = ((cfg["vocab"], W), "matrix")
+    out["final.norm"] = ((W,), "gain")
+    for i, spec in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", spec["mixer"]
+        out[p + "norm1"] = out[p + "norm1b"] = ((W,), "gain")
+        out[p + "canon1"] = ((W, cfg["canon"]["taps"]), "conv")
+        if spec["type"] == "general_delta":
+            HD = m["heads"] * m["dim"]
+            for n in "rkvga":
+                out[p + "mix." + n] = ((HD, W), "matrix")
+            out[p + "mix.a.b"] = out[p + "mix.w0"] = ((HD,), "bias")
+            out[p + "mix.w1"] = ((decay_rank, W), "matrix")
+            out[p + "mix.w2"] = ((HD, decay_rank), "matrix")
+            out[p + "mix.norm"] = ((HD,), "gain")
+            out[p + "mix.o"] = ((W, HD), "matrix")
+        else:
+            H, D, R, V, C, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            out[p + "mix.dq"] = ((Q, W), "matrix")
+            out[p + "mix.dq.norm"] = ((Q,), "gain")
+            out[p + "mix.uq"] = ((H * (D + R), Q), "matrix")
+            out[p + "mix.dkv"] = ((C + R, W), "matrix")
+            out[p + "mix.dkv.norm"] = ((C,), "gain")
+            out[p + "mix.uk"] = ((H * D, C), "matrix")
+            out[p + "mix.uv"] = ((H * V, C), "matrix")
+            out[p + "mix.sink"] = ((H,), "sink")
+            out[p + "mix.o"] = ((W, H * V), "matrix")
+        if spec.get("mlp") is not None:
+            ff = spec["mlp"]["ff"]
+            out[p + "norm2"] = out[p + "norm2b"] = ((W,), "gain")
+            out[p + "mlp.gate"] = out[p + "mlp.up"] = ((ff, W), "matrix")
+            out[p + "mlp.down"] = ((W, ff), "matrix")
+    return out
+
+
+def draw_weights(cfg: dict, seed: int, decay_rank: int = 16, sink_mean: float = 0.0) -> dict:
+    """Random weights at a scale where every mechanism matters: matrices N(0, 1/sqrt(inputs)), gains around 1,
+    biases and sinks of order 1, a convolution of order 0.5; matrices rounded to bfloat16 (as stored)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, (shape, role) in tensor_shapes(cfg, decay_rank).items():
+        n = torch.randn(shape, generator=g)
+        if role == "matrix":
+            t = n / math.sqrt(shape[1])
+        elif role == "embed":
+            t = n * 0.5
+        elif role == "gain":
+            t = 1.0 + 0.3 * n
+        elif role == "conv":
+            t = 0.5 * n
+        elif role == "sink":
+            t = sink_mean + n
+        else:
+            t = n
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def greedy(weights: dict, cfg: dict, prompt, n_new: int) -> list[int]:
+    toks, new = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(weights, cfg, toks)[-1].argmax())
+        toks.append(nxt)
+        new.append(nxt)
+    return new
