@@ -2,6 +2,7 @@
 """Benchmark: decode tokens a second of the MiniMax-M3 engine at the M2-family layer sizes.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --design guravik      (another workload: see bench_designs.py; the default one is unchanged)
 
 One JSON line on standard output.  A "step" is one decode step of the whole batch.  The default run
 has the layer sizes of the baseline's third configuration (hidden 3072, 48 q / 8 kv heads of 128,
@@ -310,6 +311,10 @@ def main() -> int:
                     help="feed the prompts of the decode runs in portions of this many tokens (0: whole)")
     ap.add_argument("--no-e2e", dest="e2e", action="store_false", help="skip the run through the Python entry point")
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
+    ap.add_argument("--design", default=None, choices=["guravik"],
+                    help="instead of the default workload: prefill and decode throughput of this design beside the "
+                         "MiniMax-M3 decoder at equal sizes, and its kernels alone against their bounds (bench_designs.py)")
+    ap.add_argument("--sizes", default="", help="with --design: the sizes to run, comma separated (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -320,6 +325,11 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design is not None:
+        import bench_designs
+        args.steps = min(args.steps, 64)
+        print(json.dumps(bench_designs.run(args)))
+        return 0
     if args.prompt_len + args.warmup + args.steps + 1 > args.context:
         ap.error(f"--context {args.context} is too short for prompts of {args.prompt_len} tokens and "
                  f"{args.warmup} + {args.steps} + 1 decoded tokens")

@@ -1,0 +1,225 @@
+"""``bench.py --design guravik``: the Guravik decoder beside the MiniMax-M3 decoder at equal sizes.
+
+For a few sizes that resemble a real model's layers (seeded random weights, bfloat16): one prompt of
+``--prompt-len`` tokens as one step (tokens a second) and decode steps of ``--batch`` requests at that
+context (tokens a second), each model through the same engine, step function and captured decode steps.
+"Equal size": the same width, layer count and vocabulary, as many attention heads of the same size, and a
+routed feed-forward whose two active experts are as wide together as the dense feed-forward.
+
+Then the new design's kernels alone, each beside the kernel of the softmax-attention model that does the
+like job, as fractions of the same peaks (measured if MEASURED_PEAKS.json is there, else the fallback):
+attention over a prompt (flops / time / tensor peak) and over single tokens (cache bytes / time / copy
+bandwidth), and the recurrence (state bytes / time / copy bandwidth for single tokens; tokens a second and
+float32 flops a second for a prompt, where it is a chain in time and has no tensor-core form here).
+Times are medians of CUDA-event intervals after warm-up; decode kernels run back to back in a CUDA graph on
+caches of several layers, larger than L2.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import random
+import statistics
+import sys
+import time
+
+SIZES = {
+    # width, layers (one latent-attention layer with a feed-forward, then two delta-rule layers without), heads ...
+    "w2048": dict(width=2048, groups=2, vocab=32000, ff=5632, attn_heads=16, dim=128, rot=64, vdim=128, q_rank=768,
+                  kv_rank=256, delta_heads=32, delta_dim=64),
+    "w4096": dict(width=4096, groups=2, vocab=32000, ff=11008, attn_heads=32, dim=128, rot=64, vdim=128, q_rank=1536,
+                  kv_rank=512, delta_heads=64, delta_dim=64),
+}
+
+
+def guravik_raw(s: dict) -> dict:
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": s["ff"]},
+              "mixer": {"heads": s["attn_heads"], "dim": s["dim"], "rot_dim": s["rot"], "vdim": s["vdim"], "q_rank": s["q_rank"],
+                        "kv_rank": s["kv_rank"], "scale": 1.0 / math.sqrt(s["dim"] + s["rot"]),
+                        "rot": {"base": 1e6, "dims": s["rot"]}}}
+    delta = {"type": "general_delta", "mixer": {"heads": s["delta_heads"], "dim": s["delta_dim"]}, "mlp": None}
+    return {"architecture": "Guravik", "vocab": s["vocab"], "width": s["width"], "layers": [latent, delta, delta] * s["groups"],
+            "canon": {"taps": 3}, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "loop": {"start": 0, "stop": 0, "times": 1}}
+
+
+def minimax_raw(s: dict) -> dict:
+    return dict(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"] // 2, num_hidden_layers=3 * s["groups"],
+                num_attention_heads=s["attn_heads"], num_key_value_heads=max(1, s["attn_heads"] // 4), head_dim=128, rotary_dim=64,
+                rope_theta=1e6, use_qk_norm=True, qk_norm_type="per_layer", num_local_experts=8, num_experts_per_tok=2,
+                use_routing_bias=True, rms_norm_eps=1e-5, tie_word_embeddings=False, architectures=["MiniMaxM3ForCausalLM"],
+                model_type="minimax_m3")
+
+
+def _model_numbers(cfg, prompt_len: int, batch: int, steps: int, warmup: int) -> dict:
+    import torch
+    from quanta_b200 import kernels
+    from quanta_b200.engine.model import random_model
+    from quanta_b200.engine.step import Engine, StepEntry
+    model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    params = sum(p.numel() for part in model.parts() for p in vars(part).values() if isinstance(p, torch.Tensor))
+    page, context = 16, prompt_len + warmup + steps + 16
+    eng = Engine(model, num_pages=(batch + 1) * -(-context // page), page_size=page, max_requests=batch + 1)
+    rng = random.Random(0)
+    V = model.spec.vocab_size
+    toks = lambda n: [rng.randrange(V) for _ in range(n)]  # noqa: E731
+    pre = []
+    for i in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p = toks(prompt_len)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepEntry(("p", i), p, (prompt_len - 1,))], end=[("p", i)])
+        b.record()
+        torch.cuda.synchronize()
+        pre.append(a.elapsed_time(b))
+    pre_ms = statistics.median(pre[2:])
+    rids = [("d", i) for i in range(batch)]
+    for rid in rids:
+        eng.step([StepEntry(rid, toks(prompt_len), ())])
+    out = torch.empty(batch, dtype=torch.int32, device="cuda:0")
+    kernels.LAUNCHES = 0
+    evs = []
+    for i in range(warmup + steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lg = eng.step([StepEntry(rid, [rng.randrange(V)], (0,)) for rid in rids])
+        kernels.sample_rows(lg, None, None, out)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    eng.check()
+    dec_ms = statistics.fmean(a.elapsed_time(b) for a, b in evs[warmup:])
+    launches = kernels.LAUNCHES // (warmup + steps)
+    stats = eng.stats()
+    del eng, model
+    torch.cuda.empty_cache()
+    return {"parameters_m": round(params / 1e6, 1), "prefill_tokens": prompt_len, "prefill_ms": round(pre_ms, 3),
+            "prefill_tok_s": round(prompt_len / pre_ms * 1e3, 1), "decode_batch": batch, "decode_ms": round(dec_ms, 4),
+            "decode_tok_s": round(batch / dec_ms * 1e3, 1), "launches_per_decode_step": int(launches),
+            "graph_replays": stats["graph_replays"]}
+
+
+# ---- kernels alone -------------------------------------------------------------------------------------
+def latent_prefill(tokens: int, heads: int, C: int, R: int, page: int = 16) -> dict:
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    pages = -(-tokens // page)
+    table = torch.randperm(pages, dtype=torch.int32).view(1, -1).to(dev)
+    cache = torch.randn(pages, 1, page, C + R, device=dev, dtype=torch.bfloat16)
+    q_lat = torch.randn(heads, tokens, C, device=dev)
+    q_rot = torch.randn(tokens, heads, R, device=dev)
+    sink = torch.zeros(heads, device=dev)
+    out = torch.empty(heads, tokens, C, device=dev, dtype=torch.bfloat16)
+    pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+    req = torch.zeros(tokens, dtype=torch.int32, device=dev)
+    st = k.new_status(dev)
+    starts = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+    ms = bk.timed(lambda: k.latent_attend(q_lat, q_rot, cache, sink, out, pos, req, table, 0.1, 1, st, req_start=starts), n=5, warm=2)
+    keys = tokens * (tokens + 1) // 2
+    flops = (2.0 * (C + R) + 2.0 * C) * heads * keys
+    return {"kernel": "latent_attend (prompt)", "tokens": tokens, "heads": heads, "latent": C, "rot": R, "ms": round(ms, 3),
+            "TFLOP/s": round(flops / ms / 1e9, 2)}
+
+
+def latent_decode(batch: int, context: int, heads: int, C: int, R: int, page: int = 16) -> dict:
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    per = -(-context // page)
+    layers = max(1, min(16, int(3e9 // (batch * per * page * (C + R) * 2))))
+    caches = [torch.randn(batch * per, 1, page, C + R, device=dev, dtype=torch.bfloat16) for _ in range(layers)]
+    table = torch.randperm(batch * per, dtype=torch.int32).view(batch, per).to(dev)
+    q_lat = torch.randn(heads, batch, C, device=dev)
+    q_rot = torch.randn(batch, heads, R, device=dev)
+    sink = torch.zeros(heads, device=dev)
+    out = torch.empty(heads, batch, C, device=dev, dtype=torch.bfloat16)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+    req = torch.arange(batch, dtype=torch.int32, device=dev)
+    st = k.new_status(dev)
+    blocks = -(-batch * heads // k.LATENT_MMA_ROWS) if k.latent_attend_uses_tensor_cores(torch.bfloat16, C, R) else batch * -(-heads // 8)
+    n_ranges = max(1, min(64, -(-296 // blocks), -(-context // 128)))
+    starts = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+
+    def all_layers():
+        for c in caches:
+            k.latent_attend(q_lat, q_rot, c, sink, out, pos, req, table, 0.1, n_ranges, st, req_start=starts)
+    ms = bk.timed_graph(all_layers, reps=1) / layers
+    nbytes = batch * context * (C + R) * 2
+    return {"kernel": "latent_attend + merge (single tokens)", "batch": batch, "context": context, "heads": heads, "latent": C,
+            "rot": R, "ranges": n_ranges, "us": round(ms * 1e3, 2), "GB/s": round(nbytes / ms / 1e6, 1)}
+
+
+def delta_rule(tokens_per_req: int, reqs: int, heads: int, D: int) -> dict:
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    T, HD = tokens_per_req * reqs, heads * D
+    proj = torch.randn(T, 4 * HD, device=dev)
+    wpre = torch.randn(T, HD, device=dev)
+    a_b, w_b = torch.zeros(HD, device=dev), torch.zeros(HD, device=dev)
+    layers = 1 if tokens_per_req > 1 else max(1, min(16, int(2e9 // (reqs * heads * D * D * 4))))
+    states = [torch.zeros(reqs, heads, D, D, device=dev) for _ in range(layers)]
+    out = torch.empty(T, heads, D, device=dev)
+    starts = torch.arange(0, T + 1, tokens_per_req, dtype=torch.int32, device=dev)
+    slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+
+    def all_layers():
+        for s in states:
+            k.delta_rule(proj, (0, HD, 2 * HD, 3 * HD), wpre, a_b, w_b, s, out, starts, slots, heads, D, math.exp(-0.5), 1e-6)
+    ms = (bk.timed_graph(all_layers, reps=1) if tokens_per_req == 1 else bk.timed(all_layers, n=5, warm=2)) / layers
+    state_bytes = 2 * reqs * heads * D * D * 4 + T * 5 * HD * 4
+    return {"kernel": "delta_rule", "requests": reqs, "tokens_per_request": tokens_per_req, "heads": heads, "dim": D,
+            "us": round(ms * 1e3, 2), "tokens/s": round(T / ms * 1e3, 1), "GB/s": round(state_bytes / ms / 1e6, 1),
+            "fp32 TFLOP/s": round(8.0 * D * D * heads * T / ms / 1e9, 2)}
+
+
+def run(args) -> dict:
+    import torch
+    import bench
+    import bench_kernels as bk
+    from quanta_b200.config import GuravikConfig, MiniMaxM3Config
+    pk, pk_src = bench.peaks()
+    clocks = bench.ClockSampler()
+    clocks.start()
+    models = {}
+    for name, s in SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        t0 = time.time()
+        g = _model_numbers(GuravikConfig.from_dict(guravik_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        m = _model_numbers(MiniMaxM3Config.from_dict(minimax_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        models[name] = {"sizes": s, "guravik": g, "minimax_m3": m}
+        print(f"[bench] {name}: guravik {g}\n[bench] {name}: minimax_m3 {m} ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+    s = SIZES["w2048"]
+    C, R, Hh = s["kv_rank"], s["rot"], s["attn_heads"]
+    T, B = args.prompt_len, args.batch
+    tensor, hbm = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    lp = latent_prefill(T, Hh, C, R)
+    sp = bk.attn_span(T, 0, Hh, max(1, Hh // 4), 128, 16)
+    ld = latent_decode(B, T, Hh, C, R)
+    sd = bk.attn_decode(B, T, Hh, max(1, Hh // 4), 128, 16)
+    dp = delta_rule(T, 1, s["delta_heads"], s["delta_dim"])
+    dd = delta_rule(1, B, s["delta_heads"], s["delta_dim"])
+    lp["frac_of_tensor_peak"] = round(lp["TFLOP/s"] * 1e12 / tensor, 4)
+    sp["frac_of_tensor_peak"] = round(sp["TFLOP/s"] * 1e12 / tensor, 4)
+    ld["frac_of_copy_bandwidth"] = round(ld["GB/s"] * 1e9 / hbm, 4)
+    if "GB/s" in sd:
+        sd["frac_of_copy_bandwidth"] = round(sd["GB/s"] * 1e9 / hbm, 4)
+    dd["frac_of_copy_bandwidth"] = round(dd["GB/s"] * 1e9 / hbm, 4)
+    kernels_alone = {"prompt_attention": {"guravik": lp, "minimax_m3": sp}, "single_token_attention": {"guravik": ld, "minimax_m3": sd},
+                     "recurrence_prompt": dp, "recurrence_single_tokens": dd}
+    for k_, v in kernels_alone.items():
+        print(f"[bench] {k_}: {v}", file=sys.stderr, flush=True)
+    first = next(iter(models.values()))["guravik"] if models else {}
+    return {"metric": f"Guravik decode tokens/s (batch {args.batch}, {args.prompt_len}-token prompts) beside MiniMax-M3 at equal sizes",
+            "value": first.get("decode_tok_s"), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": first.get("decode_ms"), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)", "design": "guravik", "models": models,
+            "kernels": kernels_alone, "peaks": {**pk, "source": pk_src}, "clocks": clocks.stop(),
+            "gpu_launches": first.get("launches_per_decode_step", 0) * args.steps, "impl": "ours"}

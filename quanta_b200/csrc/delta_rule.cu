@@ -7,12 +7,13 @@
 //   S_t = diag(w) S_{t-1} - (a * u) (u^T S_{t-1}) + k v^T     (both terms read the old state)
 //   o_t = S_t^T r
 //
-// A column j of S never meets another column, so four neighbouring lanes own one column (rows i = p,
-// p + 4, ... for lane p) in registers for the whole step, and a block owns some columns of one
-// (request, head).  Tokens are taken in chunks: the block's warps first turn a chunk's projections into
-// w, a*u, u, k, r, v in shared memory (a warp a token; the sum over k^2 is a warp reduction in a fixed
-// order), then every lane group walks the chunk's tokens without any barrier.  One token (decoding) or a
-// portion of a prompt is the same code, so a position's numbers do not depend on the cut.
+// A first kernel turns the projections of every (token, head) into w, a*u and u (all tokens at once).  The
+// recurrence itself is a chain in time.  A column j of S never meets another column, so four neighbouring
+// lanes own one column (rows i = p, p + 4, ... for lane p) in registers for the whole step, and a block owns
+// some columns of one (request, head).  Tokens are taken in chunks: w, a*u, u, k, r, v of the next chunk come
+// into shared memory by asynchronous copies while every lane group walks the chunk before without any
+// barrier.  One token (decoding) or a portion of a prompt is the same code, and a column's numbers do not
+// depend on which block owns it, so a position's numbers depend neither on the cut nor on the batch.
 //
 // A second kernel divides each head's o by its root mean square, multiplies by the gain and by
 // sigmoid(gate) and writes the activation dtype for the output projection.
@@ -22,27 +23,55 @@ constexpr int DR_LANES = 4;   // lanes that share a column
 constexpr int DR_MAX_COLS = 128;   // columns a block (512 threads), so that a lane's rows stay in registers
 template <int RPT> struct DrThreads { static constexpr int max = RPT * 16 < 512 ? RPT * 16 : 512; };
 
+// w, a*u and u of every (token, head), float32 [T, H, D] each: one warp a (token, head), the sum over k^2 a
+// warp reduction in a fixed order.
+__global__ void delta_prep_kernel(const float* __restrict__ proj, int proj_stride, int k_off, int a_off,
+                                  const float* __restrict__ wpre, const float* __restrict__ a_bias,
+                                  const float* __restrict__ w_bias, float* __restrict__ w_out,
+                                  float* __restrict__ au_out, float* __restrict__ u_out, int T, int H, int D,
+                                  float decay_scale, float unit_eps) {
+  const int lane = threadIdx.x & 31;
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (long)T * H) return;
+  const int t = (int)(wid / H), h = (int)(wid % H);
+  const float* row = proj + (size_t)t * proj_stride + (size_t)h * D;
+  const size_t base = ((size_t)t * H + h) * D;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) { const float kv = row[k_off + i]; ss += kv * kv; }
+  ss = qb_warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss + unit_eps);
+  for (int i = lane; i < D; i += 32) {
+    const float uv = row[k_off + i] * inv;
+    const float av = 1.f / (1.f + expf(-(row[a_off + i] + a_bias[h * D + i])));
+    const float sg = 1.f / (1.f + expf(-(wpre[base + i] + w_bias[h * D + i])));
+    w_out[base + i] = expf(-decay_scale * sg);
+    au_out[base + i] = av * uv;
+    u_out[base + i] = uv;
+  }
+}
+
+__device__ __forceinline__ void dr_copy4(float* dst_smem, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
 template <int RPT>            // rows of the column a lane holds: D <= 4 * RPT
 __global__ void __launch_bounds__(DrThreads<RPT>::max, 1)
-delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, int k_off, int v_off, int a_off,
-                  const float* __restrict__ wpre, const float* __restrict__ a_bias,
-                  const float* __restrict__ w_bias, float* __restrict__ state, float* __restrict__ out,
-                  const int* __restrict__ req_start, const int* __restrict__ req_slot, int H, int D,
-                  int cols_per_block, int chunk, float decay_scale, float unit_eps) {
+delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, int k_off, int v_off,
+                  const float* __restrict__ w_in, const float* __restrict__ au_in, const float* __restrict__ u_in,
+                  float* __restrict__ state, float* __restrict__ out, const int* __restrict__ req_start,
+                  const int* __restrict__ req_slot, int H, int D, int cols_per_block, int chunk) {
   extern __shared__ float sm[];
-  constexpr int DP = DR_LANES * RPT;       // padded key channels
+  constexpr int DP = DR_LANES * RPT;       // padded key channels (a power of two)
   const int r = blockIdx.x, h = blockIdx.y;
   const int col0 = blockIdx.z * cols_per_block;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int tid = threadIdx.x;
   const int p = tid % DR_LANES;
   const int j = col0 + tid / DR_LANES;
   const bool owns = (tid / DR_LANES) < cols_per_block && j < D;
-  float* s_w = sm;                          // [chunk][DP] each
-  float* s_au = s_w + (size_t)chunk * DP;
-  float* s_u = s_au + (size_t)chunk * DP;
-  float* s_k = s_u + (size_t)chunk * DP;
-  float* s_r = s_k + (size_t)chunk * DP;
-  float* s_v = s_r + (size_t)chunk * DP;
+  const size_t plane = (size_t)chunk * DP;  // one array of a chunk; six arrays a buffer, two buffers
+  // the padding rows (i >= D) are read as zeros and never written
+  for (size_t i = tid; i < 12 * plane; i += blockDim.x) sm[i] = 0.f;
 
   const int t0 = req_start[r], t1 = req_start[r + 1];
   float* S = state + ((size_t)req_slot[r] * H + h) * D * D;
@@ -52,34 +81,40 @@ delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
     const int i = p + DR_LANES * ii;
     col[ii] = (owns && i < D) ? S[(size_t)i * D + j] : 0.f;
   }
+  __syncthreads();
 
-  for (int c0 = t0; c0 < t1; c0 += chunk) {
+  // a chunk's six arrays come in by asynchronous copies while the chunk before is walked
+  auto fetch = [&](int c0, int buf) {
     const int n = min(chunk, t1 - c0);
-    __syncthreads();                        // the chunk before has been read by everyone
-    for (int tt = warp; tt < n; tt += nwarps) {
-      const float* row = proj + (size_t)(c0 + tt) * proj_stride + (size_t)h * D;
-      const float* wrow = wpre + ((size_t)(c0 + tt) * H + h) * D;
-      float ss = 0.f;
-      for (int i = lane; i < D; i += 32) { const float kv = row[k_off + i]; ss += kv * kv; }
-      ss = qb_warp_sum(ss);
-      const float inv = 1.f / sqrtf(ss + unit_eps);
-      for (int i = lane; i < DP; i += 32) {
-        float wv = 0.f, au = 0.f, uv = 0.f, kv = 0.f, rv = 0.f, vv = 0.f;
-        if (i < D) {
-          kv = row[k_off + i];
-          rv = row[r_off + i];
-          vv = row[v_off + i];
-          uv = kv * inv;
-          const float av = 1.f / (1.f + expf(-(row[a_off + i] + a_bias[h * D + i])));
-          au = av * uv;
-          const float sg = 1.f / (1.f + expf(-(wrow[i] + w_bias[h * D + i])));
-          wv = expf(-decay_scale * sg);
-        }
-        const size_t o = (size_t)tt * DP + i;
-        s_w[o] = wv; s_au[o] = au; s_u[o] = uv; s_k[o] = kv; s_r[o] = rv; s_v[o] = vv;
+    float* b = sm + (size_t)buf * 6 * plane;
+    for (int idx = tid; idx < n * DP; idx += blockDim.x) {
+      const int tt = idx / DP, i = idx % DP;
+      if (i < D) {
+        const size_t g = ((size_t)(c0 + tt) * H + h) * D + i;
+        const float* row = proj + (size_t)(c0 + tt) * proj_stride + (size_t)h * D + i;
+        dr_copy4(b + idx, w_in + g);
+        dr_copy4(b + plane + idx, au_in + g);
+        dr_copy4(b + 2 * plane + idx, u_in + g);
+        dr_copy4(b + 3 * plane + idx, row + k_off);
+        dr_copy4(b + 4 * plane + idx, row + r_off);
+        dr_copy4(b + 5 * plane + idx, row + v_off);
       }
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (t0 < t1) fetch(t0, 0);
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += chunk, buf ^= 1) {
+    const int n = min(chunk, t1 - c0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                        // this chunk has landed, and everyone is done with the other buffer
+    if (c0 + chunk < t1) fetch(c0 + chunk, buf ^ 1);
+    const float* s_w = sm + (size_t)buf * 6 * plane;
+    const float* s_au = s_w + plane;
+    const float* s_u = s_au + plane;
+    const float* s_k = s_u + plane;
+    const float* s_r = s_k + plane;
+    const float* s_v = s_r + plane;
     for (int tt = 0; tt < n; ++tt) {
       const size_t o = (size_t)tt * DP;
       float dot = 0.f;
@@ -108,15 +143,25 @@ delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
   }
 }
 
+// scratch: 3 * T * H * D floats (w, a*u, u of the step's tokens)
 extern "C" int qb_delta_rule(const float* proj, int proj_stride, int r_off, int k_off, int v_off, int a_off,
                              const float* wpre, const float* a_bias, const float* w_bias, float* state,
-                             float* out, const int* req_start, const int* req_slot, int R, int T, int H,
-                             int D, float decay_scale, float unit_eps, cudaStream_t stream) {
+                             float* out, float* scratch, const int* req_start, const int* req_slot, int R,
+                             int T, int H, int D, float decay_scale, float unit_eps, cudaStream_t stream) {
   if (R <= 0 || T <= 0) return 0;
   if (D <= 0 || D > 256 || H <= 0) return QB_ERR_UNSUPPORTED;
-  // columns a block: all of them unless that leaves most SMs idle; a multiple of 8 so that the block is whole warps
+  const size_t n = (size_t)T * H * D;
+  float *w_s = scratch, *au_s = scratch + n, *u_s = scratch + 2 * n;
+  const long warps = (long)T * H;
+  delta_prep_kernel<<<(int)((warps + 3) / 4), 128, 0, stream>>>(proj, proj_stride, k_off, a_off, wpre, a_bias, w_bias,
+                                                              w_s, au_s, u_s, T, H, D, decay_scale, unit_eps);
+  QB_LAUNCH_CHECK();
+  // columns a block: all of them (at most DR_MAX_COLS) unless that leaves most SMs idle; then fewer, down to 32
+  // where requests bring portions (the block's threads also fetch the chunks) and down to 8 where every request
+  // brings one token (the state's bytes are what counts, spread over all SMs); a multiple of 8: whole warps
+  const int min_cols = T > R ? 32 : 8;
   int splits = (D + DR_MAX_COLS - 1) / DR_MAX_COLS;
-  while ((long)R * H * splits < 132 && (D + 2 * splits - 1) / (2 * splits) >= 8) splits *= 2;
+  while ((long)R * H * splits < 132 && (D + 2 * splits - 1) / (2 * splits) >= min_cols) splits *= 2;
   int cols = (D + splits - 1) / splits;
   cols = (cols + 7) / 8 * 8;
   splits = (D + cols - 1) / cols;
@@ -124,7 +169,7 @@ extern "C" int qb_delta_rule(const float* proj, int proj_stride, int r_off, int 
   const int rpt = D <= 32 ? 8 : D <= 64 ? 16 : D <= 128 ? 32 : 64;
   const int dp = rpt * DR_LANES;
   const int chunk = dp <= 128 ? 16 : 8;
-  const size_t smem = (size_t)6 * chunk * dp * sizeof(float);
+  const size_t smem = (size_t)12 * chunk * dp * sizeof(float);
   dim3 grid(R, H, splits);
 #define DR_LAUNCH(N)                                                                                       \
   do {                                                                                                     \
@@ -133,9 +178,8 @@ extern "C" int qb_delta_rule(const float* proj, int proj_stride, int r_off, int 
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
       if (e != cudaSuccess) return (int)e;                                                                 \
     }                                                                                                      \
-    kern<<<grid, threads, smem, stream>>>(proj, proj_stride, r_off, k_off, v_off, a_off, wpre, a_bias,     \
-                                          w_bias, state, out, req_start, req_slot, H, D, cols, chunk,      \
-                                          decay_scale, unit_eps);                                          \
+    kern<<<grid, threads, smem, stream>>>(proj, proj_stride, r_off, k_off, v_off, w_s, au_s, u_s, state,   \
+                                          out, req_start, req_slot, H, D, cols, chunk);                    \
   } while (0)
   if (rpt == 8) DR_LAUNCH(8);
   else if (rpt == 16) DR_LAUNCH(16);

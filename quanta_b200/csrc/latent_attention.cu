@@ -274,3 +274,272 @@ extern "C" int qb_latent_merge(const float* part, const float* sink, void* out, 
   QB_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums), for
+// bfloat16 caches with C a multiple of 64 and R a multiple of 16.  All heads of a token read the same
+// cache rows, so the rows of a tile are (token, head) pairs of one request's portion, flattened, 16 a row
+// group: a single token with 16 heads fills an MMA tile, and a portion fills as many as it has.  A block
+// has LM_RG row groups of four warps each.  For a tile of 64 keys the four warps of a row group each take
+// 16 keys of S = Q K^T, exchange row maxima and sums through shared memory, leave P (bfloat16) there, and
+// then each take a quarter of the C channels of O += P V, V being the first C columns of the very rows K
+// was read from.  Blocks find their rows from the requests' token ranges on the device (no host list), so
+// captured decode steps run it too; a block's keys can be one of n_ranges ranges, merged afterwards.
+constexpr int LM_RG = 2;                    // row groups a block
+constexpr int LM_ROWS = 16 * LM_RG;         // (token, head) rows a block
+constexpr int LM_KEYS = 64;                 // keys a tile
+constexpr int LM_PPITCH = LM_KEYS + 8;      // row pitch of P in shared memory (elements)
+
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void lm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NT>      // n-tiles of 8 channels a warp owns in O: C = 32 * NT
+__global__ void __launch_bounds__(128 * LM_RG)
+latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot,
+                         const __nv_bfloat16* __restrict__ cache, float* __restrict__ part,
+                         const int* __restrict__ tok_pos, const int* __restrict__ req_start,
+                         const int* __restrict__ block_table, int bt_stride, int n_req, int T, int H, int R,
+                         int page_size, int num_pages, int n_ranges, float scale, int* status) {
+  constexpr int C = 32 * NT;
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  const int W = C + R, WP = W + 8;
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(lm_smem);              // [LM_ROWS][WP]
+  __nv_bfloat16* sK = sQ + (size_t)LM_ROWS * WP;                               // [LM_KEYS][WP]
+  __nv_bfloat16* sP = sK + (size_t)LM_KEYS * WP;                               // [LM_ROWS][LM_PPITCH]
+  float* sMax = reinterpret_cast<float*>(sP + (size_t)LM_ROWS * LM_PPITCH);    // [LM_RG][4][16]
+  float* sSum = sMax + LM_RG * 4 * 16;                                         // [LM_RG][4][16]
+  long long* sRow = reinterpret_cast<long long*>(sSum + LM_RG * 4 * 16);       // [LM_KEYS]
+  __shared__ int s_item[3];                                                    // request row, first flattened row, found
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rg = warp >> 2, cg = warp & 3;
+  const int range = blockIdx.y;
+  if (tid == 0) {
+    int acc = 0, found = 0;
+    for (int r = 0; r < n_req; ++r) {
+      const int rows = (req_start[r + 1] - req_start[r]) * H;
+      const int tiles = (rows + LM_ROWS - 1) / LM_ROWS;
+      if ((int)blockIdx.x < acc + tiles) { s_item[0] = r; s_item[1] = ((int)blockIdx.x - acc) * LM_ROWS; found = 1; break; }
+      acc += tiles;
+    }
+    s_item[2] = found;
+  }
+  __syncthreads();
+  if (!s_item[2]) return;
+  const int req = s_item[0], row0 = s_item[1];
+  const int t0 = req_start[req], n_rows = (req_start[req + 1] - t0) * H;
+  const int rows_here = min(LM_ROWS, n_rows - row0);
+  const int* bt = block_table + (size_t)req * bt_stride;
+  // queries: latent part and rotated part side by side, times the score scale, bfloat16; rows past the end zero
+  for (int idx = tid; idx < LM_ROWS * W; idx += blockDim.x) {
+    const int i = idx / W, c = idx % W;
+    float v = 0.f;
+    if (i < rows_here) {
+      const int tok = t0 + (row0 + i) / H, head = (row0 + i) % H;
+      v = (c < C ? q_lat[((size_t)head * T + tok) * C + c] : q_rot[((size_t)tok * H + head) * R + (c - C)]) * scale;
+    }
+    sQ[(size_t)i * WP + c] = __float2bfloat16_rn(v);
+  }
+  // the two rows of this lane in its row group's MMA tiles: lane / 4 and lane / 4 + 8
+  int my_pos[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int i = rg * 16 + (lane >> 2) + 8 * e;
+    my_pos[e] = i < rows_here ? tok_pos[t0 + (row0 + i) / H] : -1;
+  }
+  const int last_pos = tok_pos[t0 + (row0 + rows_here - 1) / H];
+  const int n_tiles = last_pos / LM_KEYS + 1;
+  const int per = (n_tiles + n_ranges - 1) / n_ranges;
+  const int tile_lo = range * per, tile_hi = min(n_tiles, tile_lo + per);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  const int chunks = W / 8;                   // 16-byte pieces of a cache row
+
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int k0 = tile * LM_KEYS;
+    __syncthreads();                          // the tile before has been read (and sQ is written)
+    if (tid < LM_KEYS) {
+      long long off = -1;
+      const int key = k0 + tid;
+      if (key <= last_pos) {
+        const int page = bt[key / page_size];
+        if (page < 0 || page >= num_pages) qb_set_status(status, QB_STATUS_BAD_PAGE, page, 3);
+        else off = ((long long)page * page_size + key % page_size) * W;
+      }
+      sRow[tid] = off;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < LM_KEYS * chunks; idx += blockDim.x) {
+      const int key = idx / chunks, c = idx % chunks;
+      const long long off = sRow[key];
+      __nv_bfloat16* dst = sK + (size_t)key * WP + c * 8;
+      if (off >= 0) {
+        const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(cache + off + c * 8) : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // S = Q K^T for this warp's 16 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const __nv_bfloat16* qa = sQ + (size_t)(rg * 16 + (lane & 15)) * WP + (lane >> 4) * 8;
+      const __nv_bfloat16* kb = sK + (size_t)(cg * 16 + (lane & 7) + (lane >> 4) * 8) * WP + ((lane >> 3) & 1) * 8;
+      for (int kk = 0; kk < W; kk += 16) {
+        uint32_t a[4], b[4];
+        lm_ldmatrix_x4(a, qa + kk);
+        lm_ldmatrix_x4(b, kb + kk);
+        lm_mma(s[0], a, b[0], b[1]);
+        lm_mma(s[1], a, b[2], b[3]);
+      }
+    }
+    // causal mask, row maxima over this warp's keys
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const int key_in = cg * 16 + nt * 8 + (lane & 3) * 2 + (v & 1);
+        const int e = v >> 1;
+        const bool ok = k0 + key_in <= my_pos[e] && sRow[key_in] >= 0;
+        s[nt][v] = ok ? s[nt][v] : -INFINITY;
+        mx[e] = fmaxf(mx[e], s[nt][v]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 1));
+      mx[e] = fmaxf(mx[e], __shfl_xor_sync(0xffffffffu, mx[e], 2));
+      if ((lane & 3) == 0) sMax[(rg * 4 + cg) * 16 + (lane >> 2) + 8 * e] = mx[e];
+    }
+    __syncthreads();
+    float corr[2], ps[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = (lane >> 2) + 8 * e;
+      float m_new = m[e];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) m_new = fmaxf(m_new, sMax[(rg * 4 + g) * 16 + row]);
+      corr[e] = (m_new == -INFINITY) ? 1.f : expf(m[e] - m_new);
+      m[e] = m_new;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float p0 = s[nt][2 * e] == -INFINITY ? 0.f : expf(s[nt][2 * e] - m[e]);
+        const float p1 = s[nt][2 * e + 1] == -INFINITY ? 0.f : expf(s[nt][2 * e + 1] - m[e]);
+        ps[e] += p0 + p1;
+        const int row = rg * 16 + (lane >> 2) + 8 * e;
+        *reinterpret_cast<__nv_bfloat162*>(sP + (size_t)row * LM_PPITCH + cg * 16 + nt * 8 + (lane & 3) * 2) =
+            __floats2bfloat162_rn(p0, p1);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      ps[e] += __shfl_xor_sync(0xffffffffu, ps[e], 1);
+      ps[e] += __shfl_xor_sync(0xffffffffu, ps[e], 2);
+      if ((lane & 3) == 0) sSum[(rg * 4 + cg) * 16 + (lane >> 2) + 8 * e] = ps[e];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = (lane >> 2) + 8 * e;
+      float add = 0.f;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) add += sSum[(rg * 4 + g) * 16 + row];
+      l[e] = l[e] * corr[e] + add;
+    }
+    // O += P V for this warp's quarter of the channels
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+    {
+      const __nv_bfloat16* pa = sP + (size_t)(rg * 16 + (lane & 15)) * LM_PPITCH + (lane >> 4) * 8;
+      const __nv_bfloat16* vb = sK + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * WP + cg * (C / 4) + (lane >> 4) * 8;
+#pragma unroll
+      for (int kk = 0; kk < LM_KEYS; kk += 16) {
+        uint32_t a[4];
+        lm_ldmatrix_x4(a, pa + kk);
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+          uint32_t b[4];
+          lm_ldmatrix_x4_trans(b, vb + (size_t)kk * WP + n * 8);
+          lm_mma(o[n], a, b[0], b[1]);
+          lm_mma(o[n + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  // partial results of this range
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int i = rg * 16 + (lane >> 2) + 8 * e;
+    if (i >= rows_here) continue;
+    const int tok = t0 + (row0 + i) / H, head = (row0 + i) % H;
+    float* dst = part + (((size_t)tok * H + head) * n_ranges + range) * (C + 2);
+    if (cg == 0 && (lane & 3) == 0) { dst[0] = m[e]; dst[1] = l[e]; }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int ch = cg * (C / 4) + n * 8 + (lane & 3) * 2;
+      dst[2 + ch] = o[n][2 * e];
+      dst[2 + ch + 1] = o[n][2 * e + 1];
+    }
+  }
+}
+
+extern "C" int qb_latent_attend_mma_supported(int C, int R) {
+  return (C == 64 || C == 128 || C == 256 || C == 512) && R >= 0 && R % 16 == 0;
+}
+
+// max_tiles: an upper bound on the row tiles of the step: sum over requests of ceil(tokens * H / 32)
+extern "C" int qb_latent_attend_mma(const float* q_lat, const float* q_rot, const void* cache, float* part,
+                                    const int* tok_pos, const int* req_start, const int* block_table,
+                                    int bt_stride, int n_req, int T, int H, int C, int R, int page_size,
+                                    int num_pages, int n_ranges, int max_tiles, float scale, int* status,
+                                    cudaStream_t stream) {
+  if (T <= 0 || n_req <= 0) return 0;
+  if (!qb_latent_attend_mma_supported(C, R) || n_ranges < 1 || page_size <= 0) return QB_ERR_UNSUPPORTED;
+  const int W = C + R, WP = W + 8;
+  const size_t smem = ((size_t)(LM_ROWS + LM_KEYS) * WP + (size_t)LM_ROWS * LM_PPITCH) * 2 + 2 * LM_RG * 4 * 16 * 4 +
+                      LM_KEYS * 8;
+  if (smem > 220 * 1024) return QB_ERR_UNSUPPORTED;
+  dim3 grid(max_tiles, n_ranges);
+#define LM_LAUNCH(N)                                                                                        \
+  do {                                                                                                      \
+    auto kern = latent_attend_mma_kernel<N>;                                                                \
+    if (smem > 48 * 1024) {                                                                                 \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      if (e != cudaSuccess) return (int)e;                                                                  \
+    }                                                                                                       \
+    kern<<<grid, 128 * LM_RG, smem, stream>>>(q_lat, q_rot, (const __nv_bfloat16*)cache, part, tok_pos,    \
+                                              req_start, block_table, bt_stride, n_req, T, H, R, page_size, \
+                                              num_pages, n_ranges, scale, status);                          \
+  } while (0)
+  if (C == 64) LM_LAUNCH(2);
+  else if (C == 128) LM_LAUNCH(4);
+  else if (C == 256) LM_LAUNCH(8);
+  else LM_LAUNCH(16);
+#undef LM_LAUNCH
+  QB_LAUNCH_CHECK();
+  return 0;
+}

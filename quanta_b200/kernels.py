@@ -516,10 +516,11 @@ def delta_rule(proj, offsets, wpre, a_bias, w_bias, state, out, req_start, req_s
         raise ValueError("delta_rule: proj rows must be dense")
     r_off, k_off, v_off, a_off = (int(o) for o in offsets)
     R = req_slot.numel()
+    scratch = torch.empty(3 * T * HD, dtype=torch.float32, device=proj.device)      # w, a*u, u of every (token, head)
     _check(lib().qb_delta_rule(ctypes.c_void_p(proj.data_ptr()), int(proj.stride(0)), r_off, k_off, v_off, a_off,
-                               _p(wpre), _p(a_bias), _p(w_bias), _p(state), _p(out), _p(req_start), _p(req_slot),
-                               R, T, n_heads, dim, ctypes.c_float(decay_scale), ctypes.c_float(unit_eps), _stream()),
-           "delta_rule")
+                               _p(wpre), _p(a_bias), _p(w_bias), _p(state), _p(out), _p(scratch), _p(req_start),
+                               _p(req_slot), R, T, n_heads, dim, ctypes.c_float(decay_scale), ctypes.c_float(unit_eps),
+                               _stream()), "delta_rule", 2)
 
 
 def head_norm_gate(o, proj, gate_off: int, gain, out, n_heads: int, dim: int, eps: float) -> None:
@@ -571,11 +572,23 @@ def latent_query(q, inv_freq, q_plain, q_rot, tok_pos, n_heads: int, dim: int, r
                                  dim, rot, int(rotated), _stream()), "latent_query")
 
 
+def latent_attend_uses_tensor_cores(cache_dtype, rank: int, rot: int) -> bool:
+    """Whether ``latent_attend`` runs these shapes on the tensor cores (bfloat16 cache, rank 64/128/256/512, rot a
+    multiple of 16) or on the CUDA cores (float32 arithmetic; every other shape, and the float32 path)."""
+    return cache_dtype == torch.bfloat16 and bool(lib().qb_latent_attend_mma_supported(int(rank), int(rot)))
+
+
+LATENT_MMA_ROWS = 32        # (token, head) rows a block of the tensor-core kernel takes
+
+
 def latent_attend(q_lat, q_rot, cache, sink, out, tok_pos, tok_req, block_table, scale: float, n_ranges: int,
-                  status) -> None:
+                  status, req_start=None, tensor_cores: bool | None = None) -> None:
     """Causal softmax attention of every token and head over the cached latent rows, with an optional sink.
     ``q_lat`` ``[heads, T, rank]``, ``q_rot`` float32 ``[T, heads, rot]``, ``out`` ``[heads, T, rank]``; each
-    token's keys are cut into ``n_ranges`` ranges that run as blocks of their own and are merged in order."""
+    token's keys are cut into ``n_ranges`` ranges that run as blocks of their own and are merged in order.
+    With ``req_start`` (int32 ``[requests + 1]``, the step's token rows of each request; token ``t`` belongs to
+    request ``tok_req[t]``) and shapes that ``latent_attend_uses_tensor_cores`` takes, the scores and sums run on
+    the tensor cores; ``tensor_cores`` False keeps them on the CUDA cores."""
     H, T, C = q_lat.shape
     num_pages, one, page_size, W = cache.shape
     R = W - C
@@ -584,8 +597,21 @@ def latent_attend(q_lat, q_rot, cache, sink, out, tok_pos, tok_req, block_table,
     if sink is not None:
         _want(sink, torch.float32, "sink")
     part = torch.empty(T * H * n_ranges * (C + 2), dtype=torch.float32, device=q_lat.device)
-    _check(lib().qb_latent_attend(_p(q_lat), _code(q_lat), _p(q_rot), _p(cache), _code(cache), _p(part), _p(tok_pos),
-                                  _p(tok_req), _p(block_table), block_table.shape[1], T, H, C, R, page_size, num_pages,
-                                  int(n_ranges), ctypes.c_float(scale), _p(status), _stream()), "latent_attend")
+    mma = (req_start is not None and q_lat.dtype == torch.float32 and tensor_cores is not False
+           and latent_attend_uses_tensor_cores(cache.dtype, C, R))
+    if tensor_cores and not mma:
+        raise ValueError("latent_attend: these shapes or dtypes do not run on the tensor cores")
+    if mma:
+        n_req = req_start.numel() - 1
+        max_tiles = -(-T * H // LATENT_MMA_ROWS) + n_req
+        _check(lib().qb_latent_attend_mma(_p(q_lat), _p(q_rot), _p(cache), _p(part), _p(tok_pos), _p(req_start),
+                                          _p(block_table), block_table.shape[1], n_req, T, H, C, R, page_size, num_pages,
+                                          int(n_ranges), max_tiles, ctypes.c_float(scale), _p(status), _stream()),
+               "latent_attend_mma")
+    else:
+        _check(lib().qb_latent_attend(_p(q_lat), _code(q_lat), _p(q_rot), _p(cache), _code(cache), _p(part), _p(tok_pos),
+                                      _p(tok_req), _p(block_table), block_table.shape[1], T, H, C, R, page_size,
+                                      num_pages, int(n_ranges), ctypes.c_float(scale), _p(status), _stream()),
+               "latent_attend")
     _check(lib().qb_latent_merge(_p(part), _p(sink), _p(out), _code(out), T, H, C, int(n_ranges), _stream()),
            "latent_merge")

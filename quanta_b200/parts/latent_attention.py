@@ -9,8 +9,11 @@ W_uv c, its score ``(q_plain . k_plain + q_rot . k_rot) * scale``; the softmax's
 The up-projections never touch the cache: ``q_plain . (W_uk c) = (W_uk^T q_plain) . c`` and
 ``sum_j p_j W_uv c_j = W_uv sum_j p_j c_j``, so the attention kernel works on the cached rows as they
 are, with every head reading the same row, and W_uk / W_uv are two batched library products on the
-step's own tokens.  Scores, softmax and the weighted sum are float32; portions of prompts and single
-tokens are the same kernels, a token's keys cut into ranges (more of them when the step has few tokens).
+step's own tokens.  Portions of prompts and single tokens are the same kernels, a token's keys cut into
+ranges (more of them when the step has few tokens).  The float32 path (and shapes the tensor-core kernel
+does not take) computes scores, softmax and the weighted sum in float32 on the CUDA cores; a bfloat16 cache
+with a latent of 64, 128, 256 or 512 and a rotated part that is a multiple of 16 runs on the tensor cores
+(bfloat16 operands, float32 sums and softmax), the rows of an MMA tile being the heads of a token.
 """
 
 from __future__ import annotations
@@ -65,11 +68,14 @@ class LatentAttention(Mixer):
     def cache_spec(self):
         return CacheSpec((CacheStream(STREAM, 1, self.C + self.R),), KeepAll())
 
-    def _ranges(self, ctx) -> int:
-        """Ranges a token's keys are cut into: one when the step has tokens enough to fill the GPU, else as
-        many as give every SM two blocks, each at least four tiles of keys long."""
-        groups = -(-self.H // 8)
-        by_work = -(-296 // max(1, ctx.n_tokens * groups))
+    def _ranges(self, ctx, tensor_cores: bool) -> int:
+        """Ranges a token's keys are cut into: one when the step has blocks enough to fill the GPU, else as
+        many as give every SM two blocks, each at least 128 keys long."""
+        if tensor_cores:
+            blocks = -(-ctx.n_tokens * self.H // kernels.LATENT_MMA_ROWS)
+        else:
+            blocks = ctx.n_tokens * -(-self.H // 8)
+        by_work = -(-296 // max(1, blocks))
         by_keys = -(-max(1, ctx.max_len_after) // 128)
         return max(1, min(64, by_work, by_keys))
 
@@ -99,8 +105,9 @@ class LatentAttention(Mixer):
         kernels.latent_query(q, inv_freq, q_plain, q_rot, ctx.tok_pos, H, self.D, self.R, rd)
         q_lat = torch.bmm(q_plain, self.w_uk, out_dtype=f32) if x.dtype != f32 else torch.bmm(q_plain, self.w_uk)
         o_lat = torch.empty((H, T, self.C), dtype=x.dtype, device=dev)
+        tc = kernels.latent_attend_uses_tensor_cores(pages.dtype, self.C, self.R)
         kernels.latent_attend(q_lat, q_rot, pages, self.sink, o_lat, ctx.tok_pos, ctx.tok_req, cache.block_table,
-                              self.scale, self._ranges(ctx), ctx.status)
+                              self.scale, self._ranges(ctx, tc), ctx.status, req_start=ctx.req_start)
         o = empty_rows(T, H * self.V, dtype=x.dtype, device=dev)
         torch.bmm(o_lat, self.w_uv_t, out=o.view(T, H, self.V).transpose(0, 1))
         return linear(o, self.w_o, out_dtype=f32)

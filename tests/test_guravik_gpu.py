@@ -45,6 +45,10 @@ CONFIGS = {
                   1, (0, 0, 1), 1.0, 1e-5), 5),
     "C": (_config(61, 48, [_delta(4, 8, ff=24), _latent(9, 8, 8, 8, 24, 16, base=100.0)], 2, (0, 2, 2), 7.5, 1e-4), 16),
     "D": (_config(77, 80, [_latent(2, 24, 16, 40, 32, 136, ff=56), _delta(2, 136)], 3, (1, 2, 2), 2.0, 1e-5), 8),
+    # latents that the tensor-core attention kernel takes in bfloat16 (64 and 128 wide, rotated parts of 16 and 32),
+    # with 5 heads (a tile of 32 rows holds six tokens and a part of the seventh) and 16 (two tokens a tile)
+    "E": (_config(111, 64, [_latent(5, 16, 16, 24, 24, 64, ff=40), _delta(2, 16), _latent(16, 8, 32, 8, 16, 128)], 3, (0, 2, 2),
+                  4.0, 1e-5), 4),
 }
 
 
@@ -117,7 +121,7 @@ def test_cuttings_agree_with_plain(models, name, dtype):
     }
     for cut, steps in cuttings.items():
         # exactly the pages the cutting needs and three state slots: both are given back and used again
-        eng = _engine(folder, dtype, steps, page_size=8 if name in "AC" else 16, slots=3)
+        eng = _engine(folder, dtype, steps, page_size=8 if name in "ACE" else 16, slots=3)
         got = H.replay(eng, steps)
         assert len(got) == len(want)
         worst, where = _worst(got, want)
@@ -387,6 +391,55 @@ def test_latent_attention_finds_one_key_among_many(dtype, n_ranges):
         want = prob @ keys[:, :C]
         tol = 1e-5 if dtype == torch.float32 else 8e-3
         assert torch.allclose(out[:, t], want, atol=tol, rtol=tol), (t, r, p, k, float((out[:, t] - want).abs().max()))
+
+
+@pytest.mark.parametrize("heads,C,R", [(16, 64, 16), (5, 128, 32), (33, 256, 16), (3, 512, 64)])
+@pytest.mark.parametrize("n_ranges", [1, 5])
+def test_latent_attention_on_the_tensor_cores(heads, C, R, n_ranges):
+    """The tensor-core kernel against a plain softmax, and against the CUDA-core kernel: single tokens of a long
+    request at positions around page and tile borders, a portion of another request and a third request of one
+    token at position 0, each query with one made key (the first, at a border, far back, its own) that
+    outweighs the rest; heads that fill a tile exactly, leave it ragged, and spill over."""
+    from quanta_b200 import kernels
+    dev, ps, dtype = "cuda:0", 16, torch.bfloat16
+    g = torch.Generator().manual_seed(heads + n_ranges)
+    rows = [(0.3 * torch.randn(n, C + R, generator=g)).to(dtype).float() for n in (700, 130, 1)]
+    queries = [(0, p, k) for p, k in ((0, 0), (15, 1), (16, 16), (17, 3), (31, 0), (32, 31), (33, 32), (63, 0), (64, 64), (65, 63),
+                                      (692, 692), (693, 640), (694, 32), (695, 31), (696, 17), (697, 16), (698, 15), (699, 0))]
+    queries += [(1, p, (p * 7) % (p + 1)) for p in range(97, 130)]
+    queries += [(2, 0, 0)]
+    T = len(queries)
+    req_start = torch.tensor([0, 18, 18 + 33, T], dtype=torch.int32, device=dev)
+    q_lat = 0.3 * torch.randn(heads, T, C, generator=g)
+    q_rot = 0.3 * torch.randn(T, heads, R, generator=g)
+    for t, (r, p, k) in enumerate(queries):
+        key = rows[r][k]
+        for h in range(heads):
+            q_lat[h, t] += (12.0 + (h % 7)) * key[:C] / key[:C].norm() ** 2
+    sink = torch.randn(heads, generator=g)
+    scale = 0.7
+    pages, table = _paged_rows(rows, ps, C + R, dtype, dev, seed=heads)
+    tok_pos = torch.tensor([p for _, p, _ in queries], dtype=torch.int32, device=dev)
+    tok_req = torch.tensor([r for r, _, _ in queries], dtype=torch.int32, device=dev)
+    status = kernels.new_status(dev)
+    assert kernels.latent_attend_uses_tensor_cores(dtype, C, R)
+    out = {}
+    for tc in (True, False):
+        o = torch.empty(heads, T, C, dtype=dtype, device=dev)
+        kernels.latent_attend(q_lat.to(dev), q_rot.to(dev), pages, sink.to(dev), o, tok_pos, tok_req, table, scale, n_ranges,
+                              status, req_start=req_start, tensor_cores=tc)
+        out[tc] = o.float().cpu()
+    assert int(status.cpu()[0]) == 0
+    qb = (q_lat * scale).to(dtype).float() / scale          # the tensor-core kernel rounds the scaled query to bfloat16
+    rb = (q_rot * scale).to(dtype).float() / scale
+    for t, (r, p, k) in enumerate(queries):
+        keys = rows[r][: p + 1]
+        s = (torch.einsum("hc,jc->hj", qb[:, t], keys[:, :C]) + torch.einsum("hr,jr->hj", rb[t], keys[:, C:])) * scale
+        prob = P.sink_softmax(s[:, None, :], sink)[:, 0]
+        assert int(prob[-1].argmax()) == k
+        want = prob @ keys[:, :C]
+        assert torch.allclose(out[True][:, t], want, atol=6e-3, rtol=2e-2), (t, r, p, k, float((out[True][:, t] - want).abs().max()))
+        assert torch.allclose(out[True][:, t], out[False][:, t], atol=1.5e-2, rtol=3e-2), (t, r, p, k)
 
 
 def test_latent_rows_are_written_normed_and_rotated():
