@@ -234,32 +234,47 @@ extern "C" int qb_latent_attend(const void* q_lat, int q_lat_dtype, const float*
 }
 
 // ---------------------------------------------------------------------------------------------
-// One warp a (token, head): top = max(sink, every range's max); denominator = exp(sink - top) + sum of the
-// ranges' sums scaled to top; out[h, t, :] = sum of the ranges' vectors scaled to top / denominator.
+// One block a (token, head): top = max(sink, every range's max); denominator = exp(sink - top) + sum of the
+// ranges' sums scaled to top; out[h, t, :] = sum of the ranges' vectors scaled to top / denominator.  The
+// first warp works out the ranges' weights (a lane a range, two for more than 32), then a thread a channel
+// adds the ranges in index order.
+constexpr int LA_MAX_RANGES = 64;
+
 template <typename A>
 __global__ void latent_merge_kernel(const float* __restrict__ part, const float* __restrict__ sink,
                                     A* __restrict__ out, int T, int H, int C, int n_ranges) {
-  const int lane = threadIdx.x & 31;
-  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wid >= (long)T * H) return;
-  const int t = (int)(wid / H), h = (int)(wid % H);
+  __shared__ float s_w[LA_MAX_RANGES];
+  __shared__ float s_inv;
+  const int t = blockIdx.x / H, h = blockIdx.x % H;
   const float* src = part + ((size_t)t * H + h) * n_ranges * (C + 2);
-  const float sk = sink ? sink[h] : -INFINITY;
-  float top = sk;
-  for (int s = 0; s < n_ranges; ++s) top = fmaxf(top, src[(size_t)s * (C + 2)]);
-  float denom = sink ? expf(sk - top) : 0.f;
-  for (int s = 0; s < n_ranges; ++s) {
-    const float ms = src[(size_t)s * (C + 2)];
-    if (ms != -INFINITY) denom += src[(size_t)s * (C + 2) + 1] * expf(ms - top);
-  }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  A* dst = out + ((size_t)h * T + t) * C;
-  for (int d = lane; d < C; d += 32) {
-    float v = 0.f;
-    for (int s = 0; s < n_ranges; ++s) {
-      const float ms = src[(size_t)s * (C + 2)];
-      if (ms != -INFINITY) v += src[(size_t)s * (C + 2) + 2 + d] * expf(ms - top);
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float ms[2], ls[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int s = lane + 32 * e;
+      ms[e] = s < n_ranges ? src[(size_t)s * (C + 2)] : -INFINITY;
+      ls[e] = s < n_ranges ? src[(size_t)s * (C + 2) + 1] : 0.f;
     }
+    const float sk = sink ? sink[h] : -INFINITY;
+    const float top = fmaxf(sk, qb_warp_max(fmaxf(ms[0], ms[1])));
+    float w[2], d = 0.f;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      w[e] = (ms[e] == -INFINITY) ? 0.f : expf(ms[e] - top);
+      d += w[e] * ls[e];
+      if (lane + 32 * e < LA_MAX_RANGES) s_w[lane + 32 * e] = w[e];
+    }
+    d = qb_warp_sum(d) + (sink ? expf(sk - top) : 0.f);
+    if (lane == 0) s_inv = d > 0.f ? 1.f / d : 0.f;
+  }
+  __syncthreads();
+  const float inv = s_inv;
+  A* dst = out + ((size_t)h * T + t) * C;
+  for (int d = threadIdx.x; d < C; d += blockDim.x) {
+    float v = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < n_ranges; ++s) v += src[(size_t)s * (C + 2) + 2 + d] * s_w[s];
     dst[d] = qb_from_float<A>(v * inv);
   }
 }
@@ -267,10 +282,10 @@ __global__ void latent_merge_kernel(const float* __restrict__ part, const float*
 extern "C" int qb_latent_merge(const float* part, const float* sink, void* out, int dtype, int T, int H, int C,
                                int n_ranges, cudaStream_t stream) {
   if (T <= 0) return 0;
-  const long warps = (long)T * H;
-  const int blocks = (int)((warps + 3) / 4);
-  QB_DISPATCH_DTYPE(dtype, A, latent_merge_kernel<A><<<blocks, 128, 0, stream>>>(part, sink, (A*)out, T, H, C,
-                                                                                n_ranges));
+  if (n_ranges < 1 || n_ranges > LA_MAX_RANGES) return QB_ERR_UNSUPPORTED;
+  const int threads = C >= 256 ? 256 : C >= 128 ? 128 : 64;
+  QB_DISPATCH_DTYPE(dtype, A, latent_merge_kernel<A><<<T * H, threads, 0, stream>>>(part, sink, (A*)out, T, H, C,
+                                                                                 n_ranges));
   QB_LAUNCH_CHECK();
   return 0;
 }
@@ -283,12 +298,13 @@ extern "C" int qb_latent_merge(const float* part, const float* sink, void* out, 
 // has LM_RG row groups of four warps each.  For a tile of 64 keys the four warps of a row group each take
 // 16 keys of S = Q K^T, exchange row maxima and sums through shared memory, leave P (bfloat16) there, and
 // then each take a quarter of the C channels of O += P V, V being the first C columns of the very rows K
-// was read from.  Blocks find their rows from the requests' token ranges on the device (no host list), so
+// was read from; the next tile's rows come in by asynchronous copies meanwhile.  Blocks find their rows from the requests' token ranges on the device (no host list), so
 // captured decode steps run it too; a block's keys can be one of n_ranges ranges, merged afterwards.
 constexpr int LM_RG = 2;                    // row groups a block
 constexpr int LM_ROWS = 16 * LM_RG;         // (token, head) rows a block
 constexpr int LM_KEYS = 64;                 // keys a tile
 constexpr int LM_PPITCH = LM_KEYS + 8;      // row pitch of P in shared memory (elements)
+static_assert(LM_RG == 2 && LM_KEYS == 64, "the tile fetch deals four of 256 threads to each of 64 rows");
 
 __device__ __forceinline__ void lm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(p);
@@ -317,11 +333,11 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
   extern __shared__ __align__(16) unsigned char lm_smem[];
   const int W = C + R, WP = W + 8;
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(lm_smem);              // [LM_ROWS][WP]
-  __nv_bfloat16* sK = sQ + (size_t)LM_ROWS * WP;                               // [LM_KEYS][WP]
-  __nv_bfloat16* sP = sK + (size_t)LM_KEYS * WP;                               // [LM_ROWS][LM_PPITCH]
+  __nv_bfloat16* sK0 = sQ + (size_t)LM_ROWS * WP;                              // [2][LM_KEYS][WP]: two tiles of keys
+  __nv_bfloat16* sP = sK0 + (size_t)2 * LM_KEYS * WP;                          // [LM_ROWS][LM_PPITCH]
   float* sMax = reinterpret_cast<float*>(sP + (size_t)LM_ROWS * LM_PPITCH);    // [LM_RG][4][16]
   float* sSum = sMax + LM_RG * 4 * 16;                                         // [LM_RG][4][16]
-  long long* sRow = reinterpret_cast<long long*>(sSum + LM_RG * 4 * 16);       // [LM_KEYS]
+  __shared__ long long sRow[2 * LM_KEYS];                                      // places of the two tiles' cache rows, -1: none
   __shared__ int s_item[3];                                                    // request row, first flattened row, found
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -344,14 +360,17 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
   const int rows_here = min(LM_ROWS, n_rows - row0);
   const int* bt = block_table + (size_t)req * bt_stride;
   // queries: latent part and rotated part side by side, times the score scale, bfloat16; rows past the end zero
-  for (int idx = tid; idx < LM_ROWS * W; idx += blockDim.x) {
-    const int i = idx / W, c = idx % W;
-    float v = 0.f;
+  for (int i = warp; i < LM_ROWS; i += (int)(blockDim.x >> 5)) {
+    __nv_bfloat16* dst = sQ + (size_t)i * WP;
     if (i < rows_here) {
       const int tok = t0 + (row0 + i) / H, head = (row0 + i) % H;
-      v = (c < C ? q_lat[((size_t)head * T + tok) * C + c] : q_rot[((size_t)tok * H + head) * R + (c - C)]) * scale;
+      const float* ql = q_lat + ((size_t)head * T + tok) * C;
+      const float* qr = q_rot + ((size_t)tok * H + head) * R;
+      for (int c = lane; c < C; c += 32) dst[c] = __float2bfloat16_rn(ql[c] * scale);
+      for (int c = lane; c < R; c += 32) dst[C + c] = __float2bfloat16_rn(qr[c] * scale);
+    } else {
+      for (int c = lane; c < W; c += 32) dst[c] = __float2bfloat16_rn(0.f);
     }
-    sQ[(size_t)i * WP + c] = __float2bfloat16_rn(v);
   }
   // the two rows of this lane in its row group's MMA tiles: lane / 4 and lane / 4 + 8
   int my_pos[2];
@@ -360,6 +379,7 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
     const int i = rg * 16 + (lane >> 2) + 8 * e;
     my_pos[e] = i < rows_here ? tok_pos[t0 + (row0 + i) / H] : -1;
   }
+  const bool rg_active = rg * 16 < rows_here;
   const int last_pos = tok_pos[t0 + (row0 + rows_here - 1) / H];
   const int n_tiles = last_pos / LM_KEYS + 1;
   const int per = (n_tiles + n_ranges - 1) / n_ranges;
@@ -371,47 +391,88 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
   for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
   const int chunks = W / 8;                   // 16-byte pieces of a cache row
 
-  for (int tile = tile_lo; tile < tile_hi; ++tile) {
-    const int k0 = tile * LM_KEYS;
-    __syncthreads();                          // the tile before has been read (and sQ is written)
+  // a tile's cache rows come in by asynchronous copies while the tile before is worked on: 64 threads look the
+  // rows' places up (lookup), a barrier later four threads a row issue its 16-byte pieces (fetch)
+  auto lookup = [&](int tile, int buf) {
     if (tid < LM_KEYS) {
       long long off = -1;
-      const int key = k0 + tid;
+      const int key = tile * LM_KEYS + tid;
       if (key <= last_pos) {
         const int page = bt[key / page_size];
         if (page < 0 || page >= num_pages) qb_set_status(status, QB_STATUS_BAD_PAGE, page, 3);
         else off = ((long long)page * page_size + key % page_size) * W;
       }
-      sRow[tid] = off;
+      sRow[buf * LM_KEYS + tid] = off;
     }
-    __syncthreads();
-    for (int idx = tid; idx < LM_KEYS * chunks; idx += blockDim.x) {
-      const int key = idx / chunks, c = idx % chunks;
-      const long long off = sRow[key];
-      __nv_bfloat16* dst = sK + (size_t)key * WP + c * 8;
-      if (off >= 0) {
-        const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(cache + off + c * 8) : "memory");
-      } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+  };
+  auto fetch = [&](int buf) {
+    const int key_in = tid >> 2;              // 256 threads: four a row
+    const long long off = sRow[buf * LM_KEYS + key_in];
+    __nv_bfloat16* dst = sK0 + ((size_t)buf * LM_KEYS + key_in) * WP;
+    if (off >= 0) {
+      const __nv_bfloat16* src = cache + off;
+      for (int c = tid & 3; c < chunks; c += 4) {
+        const unsigned d = (unsigned)__cvta_generic_to_shared(dst + c * 8);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + c * 8) : "memory");
       }
+    } else {
+      for (int c = tid & 3; c < chunks; c += 4) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  };
+  // the first two tiles are asked for at once; after that tile i + 1 is asked for as soon as tile i has landed
+  // (its buffer was read last by tile i - 1), its rows' places having been looked up during tile i - 1
+  if (tile_lo < tile_hi) {
+    lookup(tile_lo, 0);
+    if (tile_lo + 1 < tile_hi) lookup(tile_lo + 1, 1);
     __syncthreads();
+    fetch(0);
+    if (tile_lo + 1 < tile_hi) fetch(1);
+  }
+  int buf = 0;
+  for (int tile = tile_lo; tile < tile_hi; ++tile, buf ^= 1) {
+    const int k0 = tile * LM_KEYS;
+    if (tile == tile_lo && tile + 1 < tile_hi) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                          // this tile has landed; the tile before has been read (and sQ is written)
+    if (tile > tile_lo && tile + 1 < tile_hi) fetch(buf ^ 1);
+    const __nv_bfloat16* sK = sK0 + (size_t)buf * LM_KEYS * WP;
 
-    // S = Q K^T for this warp's 16 keys
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // S = Q K^T for this warp's 16 keys: the fragments of the next 16 channels are asked for before the MMAs of
+    // these, and even and odd steps add into accumulators of their own (two chains of MMAs instead of one)
+    float s[2][4];
     {
+      float acc[2][2][4];
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int y = 0; y < 2; ++y) { acc[x][y][0] = acc[x][y][1] = acc[x][y][2] = acc[x][y][3] = 0.f; }
       const __nv_bfloat16* qa = sQ + (size_t)(rg * 16 + (lane & 15)) * WP + (lane >> 4) * 8;
       const __nv_bfloat16* kb = sK + (size_t)(cg * 16 + (lane & 7) + (lane >> 4) * 8) * WP + ((lane >> 3) & 1) * 8;
-      for (int kk = 0; kk < W; kk += 16) {
-        uint32_t a[4], b[4];
-        lm_ldmatrix_x4(a, qa + kk);
-        lm_ldmatrix_x4(b, kb + kk);
-        lm_mma(s[0], a, b[0], b[1]);
-        lm_mma(s[1], a, b[2], b[3]);
+      uint32_t a0[4], b0[4], a1[4], b1[4];
+      lm_ldmatrix_x4(a0, qa);
+      lm_ldmatrix_x4(b0, kb);
+      int kk = rg_active ? 0 : W;             // a row group without rows (a single token of few heads) skips the MMAs
+      for (; kk + 32 <= W; kk += 32) {
+        lm_ldmatrix_x4(a1, qa + kk + 16);
+        lm_ldmatrix_x4(b1, kb + kk + 16);
+        lm_mma(acc[0][0], a0, b0[0], b0[1]);
+        lm_mma(acc[0][1], a0, b0[2], b0[3]);
+        if (kk + 32 < W) {
+          lm_ldmatrix_x4(a0, qa + kk + 32);
+          lm_ldmatrix_x4(b0, kb + kk + 32);
+        }
+        lm_mma(acc[1][0], a1, b1[0], b1[1]);
+        lm_mma(acc[1][1], a1, b1[2], b1[3]);
       }
+      if (kk < W) {                           // an odd number of steps: the last fragments are in a0, b0
+        lm_mma(acc[0][0], a0, b0[0], b0[1]);
+        lm_mma(acc[0][1], a0, b0[2], b0[3]);
+      }
+#pragma unroll
+      for (int y = 0; y < 2; ++y)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) s[y][v] = acc[0][y][v] + acc[1][y][v];
     }
     // causal mask, row maxima over this warp's keys
     float mx[2] = {-INFINITY, -INFINITY};
@@ -421,7 +482,7 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
       for (int v = 0; v < 4; ++v) {
         const int key_in = cg * 16 + nt * 8 + (lane & 3) * 2 + (v & 1);
         const int e = v >> 1;
-        const bool ok = k0 + key_in <= my_pos[e] && sRow[key_in] >= 0;
+        const bool ok = k0 + key_in <= my_pos[e];
         s[nt][v] = ok ? s[nt][v] : -INFINITY;
         mx[e] = fmaxf(mx[e], s[nt][v]);
       }
@@ -462,6 +523,7 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
       if ((lane & 3) == 0) sSum[(rg * 4 + cg) * 16 + (lane >> 2) + 8 * e] = ps[e];
     }
     __syncthreads();
+    if (tile + 2 < tile_hi) lookup(tile + 2, buf);      // this tile's places were used when it was asked for
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = (lane >> 2) + 8 * e;
@@ -473,7 +535,7 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
     // O += P V for this warp's quarter of the channels
 #pragma unroll
     for (int n = 0; n < NT; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
-    {
+    if (rg_active) {
       const __nv_bfloat16* pa = sP + (size_t)(rg * 16 + (lane & 15)) * LM_PPITCH + (lane >> 4) * 8;
       const __nv_bfloat16* vb = sK + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * WP + cg * (C / 4) + (lane >> 4) * 8;
 #pragma unroll
@@ -520,8 +582,7 @@ extern "C" int qb_latent_attend_mma(const float* q_lat, const float* q_rot, cons
   if (T <= 0 || n_req <= 0) return 0;
   if (!qb_latent_attend_mma_supported(C, R) || n_ranges < 1 || page_size <= 0) return QB_ERR_UNSUPPORTED;
   const int W = C + R, WP = W + 8;
-  const size_t smem = ((size_t)(LM_ROWS + LM_KEYS) * WP + (size_t)LM_ROWS * LM_PPITCH) * 2 + 2 * LM_RG * 4 * 16 * 4 +
-                      LM_KEYS * 8;
+  const size_t smem = ((size_t)(LM_ROWS + 2 * LM_KEYS) * WP + (size_t)LM_ROWS * LM_PPITCH) * 2 + 2 * LM_RG * 4 * 16 * 4;
   if (smem > 220 * 1024) return QB_ERR_UNSUPPORTED;
   dim3 grid(max_tiles, n_ranges);
 #define LM_LAUNCH(N)                                                                                        \
