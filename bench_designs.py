@@ -223,3 +223,23 @@ def run(args) -> dict:
             "data": "synthetic (seeded uniform token ids, seeded random weights)", "design": "guravik", "models": models,
             "kernels": kernels_alone, "peaks": {**pk, "source": pk_src}, "clocks": clocks.stop(),
             "gpu_launches": first.get("launches_per_decode_step", 0) * args.steps, "impl": "ours"}
+
+
+if __name__ == "__main__":
+    # one kernel alone, one JSON line:  python bench_designs.py latent_prefill --tokens 1024
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["latent_prefill", "latent_decode", "delta_rule"])
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--latent", type=int, default=256)
+    ap.add_argument("--rot", type=int, default=64)
+    ap.add_argument("--dim", type=int, default=64)
+    a = ap.parse_args()
+    if a.kernel == "latent_prefill":
+        print(json.dumps(latent_prefill(a.tokens, a.heads, a.latent, a.rot)))
+    elif a.kernel == "latent_decode":
+        print(json.dumps(latent_decode(a.batch, a.tokens, a.heads, a.latent, a.rot)))
+    else:
+        print(json.dumps(delta_rule(a.tokens, a.batch, a.heads, a.dim)))

@@ -8,8 +8,8 @@
 //   o_t = S_t^T r
 //
 // A first kernel turns the projections of every (token, head) into w, a*u and u (all tokens at once).  The
-// recurrence itself is a chain in time.  A column j of S never meets another column, so four neighbouring
-// lanes own one column (rows i = p, p + 4, ... for lane p) in registers for the whole step, and a block owns
+// recurrence itself is a chain in time.  A column j of S never meets another column, so eight neighbouring
+// lanes own one column (rows i = p, p + 8, ... for lane p) in registers for the whole step, and a block owns
 // some columns of one (request, head).  Tokens are taken in chunks: w, a*u, u, k, r, v of the next chunk come
 // into shared memory by asynchronous copies while every lane group walks the chunk before without any
 // barrier.  One token (decoding) or a portion of a prompt is the same code, and a column's numbers do not
@@ -19,9 +19,9 @@
 // sigmoid(gate) and writes the activation dtype for the output projection.
 #include "common.cuh"
 
-constexpr int DR_LANES = 4;   // lanes that share a column
-constexpr int DR_MAX_COLS = 128;   // columns a block (512 threads), so that a lane's rows stay in registers
-template <int RPT> struct DrThreads { static constexpr int max = RPT * 16 < 512 ? RPT * 16 : 512; };
+constexpr int DR_LANES = 8;   // lanes that share a column
+constexpr int DR_MAX_COLS = 64;    // columns a block (512 threads), so that a lane's rows stay in registers
+template <int RPT> struct DrThreads { static constexpr int max = RPT * 64 < 512 ? RPT * 64 : 512; };
 
 // w, a*u and u of every (token, head), float32 [T, H, D] each: one warp a (token, head), the sum over k^2 a
 // warp reduction in a fixed order.
@@ -55,7 +55,7 @@ __device__ __forceinline__ void dr_copy4(float* dst_smem, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int RPT>            // rows of the column a lane holds: D <= 4 * RPT
+template <int RPT>            // rows of the column a lane holds: D <= DR_LANES * RPT
 __global__ void __launch_bounds__(DrThreads<RPT>::max, 1)
 delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, int k_off, int v_off,
                   const float* __restrict__ w_in, const float* __restrict__ au_in, const float* __restrict__ u_in,
@@ -122,6 +122,7 @@ delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
       for (int ii = 0; ii < RPT; ++ii) dot += s_u[o + p + DR_LANES * ii] * col[ii];
       dot += __shfl_xor_sync(0xffffffffu, dot, 1);
       dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
       const float vj = owns ? s_v[o + j] : 0.f;
       float acc = 0.f;
 #pragma unroll
@@ -133,6 +134,7 @@ delta_rule_kernel(const float* __restrict__ proj, int proj_stride, int r_off, in
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       if (owns && p == 0) out[((size_t)(c0 + tt) * H + h) * D + j] = acc;
     }
   }
@@ -156,17 +158,17 @@ extern "C" int qb_delta_rule(const float* proj, int proj_stride, int r_off, int 
   delta_prep_kernel<<<(int)((warps + 3) / 4), 128, 0, stream>>>(proj, proj_stride, k_off, a_off, wpre, a_bias, w_bias,
                                                               w_s, au_s, u_s, T, H, D, decay_scale, unit_eps);
   QB_LAUNCH_CHECK();
-  // columns a block: all of them (at most DR_MAX_COLS) unless that leaves most SMs idle; then fewer, down to 32
-  // where requests bring portions (the block's threads also fetch the chunks) and down to 8 where every request
-  // brings one token (the state's bytes are what counts, spread over all SMs); a multiple of 8: whole warps
-  const int min_cols = T > R ? 32 : 8;
+  // columns a block: all of them (at most DR_MAX_COLS) unless that leaves most SMs idle; then fewer, down to 16
+  // where requests bring portions (the block's threads also fetch the chunks) and down to 4 where every request
+  // brings one token (the state's bytes are what counts, spread over all SMs); a multiple of 4: whole warps
+  const int min_cols = T > R ? 16 : 4;
   int splits = (D + DR_MAX_COLS - 1) / DR_MAX_COLS;
   while ((long)R * H * splits < 132 && (D + 2 * splits - 1) / (2 * splits) >= min_cols) splits *= 2;
   int cols = (D + splits - 1) / splits;
-  cols = (cols + 7) / 8 * 8;
+  cols = (cols + 3) / 4 * 4;
   splits = (D + cols - 1) / cols;
   const int threads = cols * DR_LANES;
-  const int rpt = D <= 32 ? 8 : D <= 64 ? 16 : D <= 128 ? 32 : 64;
+  const int rpt = D <= 32 ? 4 : D <= 64 ? 8 : D <= 128 ? 16 : 32;
   const int dp = rpt * DR_LANES;
   const int chunk = dp <= 128 ? 16 : 8;
   const size_t smem = (size_t)12 * chunk * dp * sizeof(float);
@@ -181,10 +183,10 @@ extern "C" int qb_delta_rule(const float* proj, int proj_stride, int r_off, int 
     kern<<<grid, threads, smem, stream>>>(proj, proj_stride, r_off, k_off, v_off, w_s, au_s, u_s, state,   \
                                           out, req_start, req_slot, H, D, cols, chunk);                    \
   } while (0)
-  if (rpt == 8) DR_LAUNCH(8);
+  if (rpt == 4) DR_LAUNCH(4);
+  else if (rpt == 8) DR_LAUNCH(8);
   else if (rpt == 16) DR_LAUNCH(16);
-  else if (rpt == 32) DR_LAUNCH(32);
-  else DR_LAUNCH(64);
+  else DR_LAUNCH(32);
 #undef DR_LAUNCH
   QB_LAUNCH_CHECK();
   return 0;

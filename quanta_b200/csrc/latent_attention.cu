@@ -393,12 +393,17 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
 
   // a tile's cache rows come in by asynchronous copies while the tile before is worked on: 64 threads look the
   // rows' places up (lookup), a barrier later four threads a row issue its 16-byte pieces (fetch)
-  auto lookup = [&](int tile, int buf) {
+  // lookup_ask reads the table entry of this thread's row of a tile (the load is not waited for), lookup_put
+  // turns it into the row's place later, when the entry has long arrived
+  auto lookup_ask = [&](int tile) -> int {
+    const int key = tile * LM_KEYS + tid;
+    return (tid < LM_KEYS && key <= last_pos) ? bt[key / page_size] : -2;
+  };
+  auto lookup_put = [&](int tile, int buf, int page) {
     if (tid < LM_KEYS) {
       long long off = -1;
       const int key = tile * LM_KEYS + tid;
-      if (key <= last_pos) {
-        const int page = bt[key / page_size];
+      if (page != -2) {
         if (page < 0 || page >= num_pages) qb_set_status(status, QB_STATUS_BAD_PAGE, page, 3);
         else off = ((long long)page * page_size + key % page_size) * W;
       }
@@ -423,8 +428,8 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
   // the first two tiles are asked for at once; after that tile i + 1 is asked for as soon as tile i has landed
   // (its buffer was read last by tile i - 1), its rows' places having been looked up during tile i - 1
   if (tile_lo < tile_hi) {
-    lookup(tile_lo, 0);
-    if (tile_lo + 1 < tile_hi) lookup(tile_lo + 1, 1);
+    lookup_put(tile_lo, 0, lookup_ask(tile_lo));
+    if (tile_lo + 1 < tile_hi) lookup_put(tile_lo + 1, 1, lookup_ask(tile_lo + 1));
     __syncthreads();
     fetch(0);
     if (tile_lo + 1 < tile_hi) fetch(1);
@@ -436,6 +441,7 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
     else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                          // this tile has landed; the tile before has been read (and sQ is written)
     if (tile > tile_lo && tile + 1 < tile_hi) fetch(buf ^ 1);
+    const int page_ahead = tile + 2 < tile_hi ? lookup_ask(tile + 2) : -2;
     const __nv_bfloat16* sK = sK0 + (size_t)buf * LM_KEYS * WP;
 
     // S = Q K^T for this warp's 16 keys: the fragments of the next 16 channels are asked for before the MMAs of
@@ -523,7 +529,7 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
       if ((lane & 3) == 0) sSum[(rg * 4 + cg) * 16 + (lane >> 2) + 8 * e] = ps[e];
     }
     __syncthreads();
-    if (tile + 2 < tile_hi) lookup(tile + 2, buf);      // this tile's places were used when it was asked for
+    if (tile + 2 < tile_hi) lookup_put(tile + 2, buf, page_ahead);   // this tile's places were used when it was asked for
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = (lane >> 2) + 8 * e;
@@ -543,11 +549,16 @@ latent_attend_mma_kernel(const float* __restrict__ q_lat, const float* __restric
         uint32_t a[4];
         lm_ldmatrix_x4(a, pa + kk);
 #pragma unroll
-        for (int n = 0; n < NT; n += 2) {
-          uint32_t b[4];
-          lm_ldmatrix_x4_trans(b, vb + (size_t)kk * WP + n * 8);
-          lm_mma(o[n], a, b[0], b[1]);
-          lm_mma(o[n + 1], a, b[2], b[3]);
+        for (int n = 0; n < NT; n += 4) {     // the fragments of four channel tiles are asked for before their MMAs
+          uint32_t b0[4], b1[4];
+          lm_ldmatrix_x4_trans(b0, vb + (size_t)kk * WP + n * 8);
+          if (n + 2 < NT) lm_ldmatrix_x4_trans(b1, vb + (size_t)kk * WP + (n + 2) * 8);
+          lm_mma(o[n], a, b0[0], b0[1]);
+          lm_mma(o[n + 1], a, b0[2], b0[3]);
+          if (n + 2 < NT) {
+            lm_mma(o[n + 2], a, b1[0], b1[1]);
+            lm_mma(o[n + 3], a, b1[2], b1[3]);
+          }
         }
       }
     }
