@@ -221,7 +221,7 @@ extern "C" int qb_latent_attend(const void* q_lat, int q_lat_dtype, const float*
   dim3 grid(T, (H + hpb - 1) / hpb, n_ranges);
   QB_DISPATCH_DTYPE(dtype, A, QB_DISPATCH_DTYPE(q_lat_dtype, QL, {
     auto kern = latent_attend_kernel<A, QL>;
-    if (smem > 48 * 1024) {
+    if (smem + 2048 > 48 * 1024) {   /* the kernel also has some static shared memory */
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
@@ -599,7 +599,7 @@ extern "C" int qb_latent_attend_mma(const float* q_lat, const float* q_rot, cons
 #define LM_LAUNCH(N)                                                                                        \
   do {                                                                                                      \
     auto kern = latent_attend_mma_kernel<N>;                                                                \
-    if (smem > 48 * 1024) {                                                                                 \
+    if (smem + 2048 > 48 * 1024) {   /* the kernel also has some static shared memory */                                                                                 \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                                  \
     }                                                                                                       \

@@ -393,7 +393,8 @@ def test_latent_attention_finds_one_key_among_many(dtype, n_ranges):
         assert torch.allclose(out[:, t], want, atol=tol, rtol=tol), (t, r, p, k, float((out[:, t] - want).abs().max()))
 
 
-@pytest.mark.parametrize("heads,C,R", [(16, 64, 16), (5, 128, 32), (33, 256, 16), (3, 512, 64)])
+# (4, 64, 64): the kernel's dynamic shared memory is exactly 48 KB, beside which it has static shared memory
+@pytest.mark.parametrize("heads,C,R", [(16, 64, 16), (5, 128, 32), (33, 256, 16), (3, 512, 64), (4, 64, 64)])
 @pytest.mark.parametrize("n_ranges", [1, 5])
 def test_latent_attention_on_the_tensor_cores(heads, C, R, n_ranges):
     """The tensor-core kernel against a plain softmax, and against the CUDA-core kernel: single tokens of a long
