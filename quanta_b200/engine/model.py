@@ -31,6 +31,11 @@ def parse_dtype(d) -> torch.dtype:
         raise ValueError(f"dtype {d!r}: choose bfloat16 or float32") from None
 
 
+def _plain(pending):
+    """A pending contribution as a tensor (one that is normed first is normed now)."""
+    return pending.materialize() if hasattr(pending, "materialize") else pending
+
+
 def _walk(part: Part):
     yield part
     for c in part.children():
@@ -111,14 +116,14 @@ class Model:
             if entry.add_embedding:
                 # the stream so far, then the embedded tokens once more, both summed in float32
                 if pending is not None:
-                    kernels.residual_add(h, pending)
+                    kernels.residual_add(h, _plain(pending))
                     pending = None
                 kernels.residual_add(h, embedded)
             pending = self.blocks[entry.layer].forward(h, pending, ctx, caches[pos], states[pos])
             if self.residual_trace is not None:
                 now = h.clone()
                 if pending is not None:
-                    kernels.residual_add(now, pending)
+                    kernels.residual_add(now, _plain(pending))
                 self.residual_trace.append(now)
         if want_rows is None or want_rows.numel() == 0:
             return None

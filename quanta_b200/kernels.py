@@ -135,6 +135,29 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
                                 ctypes.c_float(eps), int(store_h), _stream()), "add_rmsnorm")
 
 
+def normed_add_rmsnorm(h: torch.Tensor, y: torch.Tensor, y_gain: torch.Tensor, y_eps: float, weight: torch.Tensor,
+                       eps: float, out: torch.Tensor | None, rows: torch.Tensor | None = None, store_h: bool = True) -> None:
+    """``h += y_gain * y * rsqrt(mean(y^2) + y_eps)`` (float32) and ``out = weight * h * rsqrt(mean(h^2) + eps)``: a
+    sublayer's output that is normed before it joins the stream, and the norm that follows, in one launch.
+    ``y`` float32 ``[T, H]``; ``rows`` / ``store_h`` / ``out`` None as in ``add_rmsnorm``."""
+    for t, n in ((h, "h"), (y, "y"), (y_gain, "y_gain")):
+        _want(t, torch.float32, n)
+    T, H = h.shape
+    if tuple(y.shape) != (T, H) or y_gain.numel() != H:
+        raise ValueError("normed_add_rmsnorm: shape mismatch")
+    n = T if rows is None else rows.numel()
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    if out is not None:
+        _want(weight, torch.float32, "weight")
+        if out.shape[0] != n or out.shape[1] != H or weight.numel() != H:
+            raise ValueError("normed_add_rmsnorm: out or weight shape mismatch")
+    _check(lib().qb_normed_add_rmsnorm(_p(h), _p(y), _p(y_gain), ctypes.c_float(y_eps),
+                                       _p(weight) if out is not None else ctypes.c_void_p(0), _p(out),
+                                       _code(out) if out is not None else F32, _p(rows), n, H, ctypes.c_float(eps),
+                                       int(store_h), _stream()), "normed_add_rmsnorm")
+
+
 def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
     """``h += sum_s delta[:, s]`` in float32 (``delta`` ``[T, H]`` or ``[T, S, H]``), without a norm."""
     _want(h, torch.float32, "h")

@@ -188,8 +188,25 @@ class Part:
         return []
 
 
+class NormedPending:
+    """A pending contribution that is normed before it joins the residual stream: ``y`` (float32 ``[T, H]``, a
+    sublayer's output) and the norm part that is applied to it.  A norm that gets one as its ``delta`` norms
+    ``y``, adds it and norms the sum in one launch when it can (``Norm.forward`` of the built-in norms); whoever
+    needs the plain numbers calls ``materialize``."""
+
+    def __init__(self, y: torch.Tensor, norm: "Norm"):
+        self.y = y if y.dtype == torch.float32 else y.float()
+        self.norm = norm
+
+    def materialize(self) -> torch.Tensor:
+        d = torch.empty(self.y.shape, dtype=torch.float32, device=self.y.device)
+        self.norm.forward(self.y, None, d)
+        return d
+
+
 class Norm(Part):
     def forward(self, h: torch.Tensor, delta, out, rows=None, store_h=True) -> None:
+        """``delta``: None, a tensor ``[T, H]`` / ``[T, S, H]``, or a ``NormedPending``."""
         raise NotImplementedError
 
 

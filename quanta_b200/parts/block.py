@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels
 from ..matmul import empty_rows, linear
-from .base import Block, Embedding, Head, TensorSpec, make, register
+from .base import Block, Embedding, Head, NormedPending, TensorSpec, make, register
 
 
 @register("block", "pre_norm")
@@ -42,8 +42,8 @@ class SandwichNormBlock(Block):
     """A norm before and a norm after each sublayer: ``h += post_1(mixer(conv(pre_1(h))))`` and, where the
     layer has a feed-forward, ``h += post_2(feed_forward(pre_2(h)))``.  ``conv`` (optional) is a short
     convolution over time on the mixer's input; its last inputs are part of the layer's per-request state.
-    Both sums are float32 and happen inside the next pre-norm (or the head's norm); the post-norms write
-    float32, so a sublayer's contribution is never rounded to the activation dtype."""
+    Both sums are float32 and happen inside the next pre-norm (or the head's norm), which also applies the
+    post-norm to the sublayer's float32 output: a contribution is never rounded to the activation dtype."""
 
     graph_safe = True
 
@@ -74,13 +74,6 @@ class SandwichNormBlock(Block):
                 spec[name] = need
         return spec
 
-    def _post(self, norm, y):
-        if y.dtype != torch.float32:
-            y = y.float()
-        d = torch.empty(y.shape, dtype=torch.float32, device=y.device)
-        norm.forward(y, None, d)
-        return d
-
     def forward(self, h, pending, ctx, cache, state):
         T = h.shape[0]
         x = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
@@ -90,12 +83,14 @@ class SandwichNormBlock(Block):
             normed = torch.empty((T, self.hidden), dtype=torch.float32, device=h.device)
             self.mixer_norm.forward(h, pending, normed)
             self.conv.forward(normed, ctx, state, x)
-        d = self._post(self.mixer_post_norm, self.mixer.forward(x, ctx, cache, state))
+        # a sublayer's output stays pending together with its post-norm: the next pre-norm (or the head's norm)
+        # norms it, adds it to the stream and norms the sum in one launch
+        d = NormedPending(self.mixer.forward(x, ctx, cache, state), self.mixer_post_norm)
         if self.feed_forward is None:
             return d
         x2 = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
         self.feed_forward_norm.forward(h, d, x2)
-        return self._post(self.feed_forward_post_norm, self.feed_forward.forward(x2, ctx))
+        return NormedPending(self.feed_forward.forward(x2, ctx), self.feed_forward_post_norm)
 
 
 @register("embedding", "token_table")

@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import Norm, TensorSpec, register
+from .base import Norm, NormedPending, TensorSpec, register
 
 
 @register("norm", "rms_norm")
@@ -25,4 +25,11 @@ class RMSNorm(Norm):
         self.weight = fetch(self.weight_name)
 
     def forward(self, h, delta, out, rows=None, store_h=True):
+        if isinstance(delta, NormedPending):
+            if isinstance(delta.norm, RMSNorm):
+                # the norm of the sublayer's output, the sum and this norm in one launch
+                kernels.normed_add_rmsnorm(h, delta.y, delta.norm.weight, delta.norm.eps, self.weight, self.eps, out,
+                                           rows=rows, store_h=store_h)
+                return
+            delta = delta.materialize()
         kernels.add_rmsnorm(h, delta, self.weight, self.eps, out, rows=rows, store_h=store_h)

@@ -330,6 +330,29 @@ def test_delta_rule_alone(dim, heads):
     assert float(state[1].min()) == 5.0
 
 
+@pytest.mark.parametrize("width", [48, 256, 1000])
+def test_post_norm_and_next_norm_in_one_launch(width):
+    """A sublayer's output normed, added to the stream and the sum normed, in one kernel: against plain arithmetic,
+    for all rows and for chosen rows that leave the stream as it is."""
+    from quanta_b200 import kernels
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(width)
+    T = 9
+    h, y = torch.randn(T, width, generator=g) * 3, torch.randn(T, width, generator=g) * 0.01
+    gy, w = 1 + 0.3 * torch.randn(width, generator=g), 1 + 0.3 * torch.randn(width, generator=g)
+    summed = h + P.rms_norm(y, gy, 1e-6)
+    want = P.rms_norm(summed, w, 1e-5)
+    for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1e-2)):
+        hd, out = h.to(dev), torch.empty(T, width, dtype=dtype, device=dev)
+        kernels.normed_add_rmsnorm(hd, y.to(dev), gy.to(dev), 1e-6, w.to(dev), 1e-5, out)
+        assert torch.allclose(hd.cpu(), summed, atol=1e-6, rtol=1e-6)
+        assert torch.allclose(out.float().cpu(), want, atol=tol, rtol=tol)
+    rows = torch.tensor([7, 2], dtype=torch.int32, device=dev)
+    hd, out = h.to(dev), torch.empty(2, width, device=dev)
+    kernels.normed_add_rmsnorm(hd, y.to(dev), gy.to(dev), 1e-6, w.to(dev), 1e-5, out, rows=rows, store_h=False)
+    assert torch.equal(hd.cpu(), h) and torch.allclose(out.cpu(), want[[7, 2]], atol=2e-6, rtol=2e-6)
+
+
 def _paged_rows(rows_per_req, page_size, width, dtype, dev, seed):
     """Cache pages in a shuffled order holding ``rows_per_req`` (a list of [n, width] tensors)."""
     need = [-(-r.shape[0] // page_size) for r in rows_per_req]
