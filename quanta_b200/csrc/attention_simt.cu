@@ -8,6 +8,8 @@
 //
 //   s = (q . k) * scale;  softmax over keys in float32;  out = P V
 //   (src/quanta/minimax/attention.py:194-203; grouped heads: q head h reads kv head h / (nq/nkv))
+// Keys (and queries) have `hd` elements a head, values and outputs `vd`; any positive sizes up to 256 (rows
+// whose size is no multiple of the 16-byte vector are read element by element).
 //
 // One warp per (token, q head): lanes own keys for the scores, then own dims for P V.
 #include "common.cuh"
@@ -40,8 +42,8 @@ template <typename A>
 __global__ void paged_attention_simt_kernel(
     const A* __restrict__ q, const A* __restrict__ k_cache, const A* __restrict__ v_cache,
     A* __restrict__ out, const int* __restrict__ tok_pos, const int* __restrict__ tok_req,
-    const int* __restrict__ block_table, int bt_stride, int T, int nq, int nkv, int hd, int page_size,
-    int num_pages, float scale, int window, int* status) {
+    const int* __restrict__ block_table, int bt_stride, int T, int nq, int nkv, int hd, int vd, int page_size,
+    int num_pages, float scale, int window, int vec, int* status) {
   extern __shared__ float qs_all[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long wid = (long)blockIdx.x * ATT_WARPS + warp;
@@ -66,20 +68,24 @@ __global__ void paged_attention_simt_kernel(
     const int key = kb + lane;
     const bool valid = key >= lo && key <= pos;
     float s = -INFINITY;
-    long base = -1;     // element offset of this lane's key row (K and V share the layout)
+    long base = -1;     // index of this lane's key row among all (page, kv head, slot) rows, in K and in V
     if (valid) {
       const int page = bt[key / page_size];
       if (page < 0 || page >= num_pages) {
         qb_set_status(status, QB_STATUS_BAD_PAGE, page, 3);
       } else {
-        base = (((long)page * nkv + kvh) * page_size + key % page_size) * hd;
-        const A* kp = k_cache + base;
+        base = ((long)page * nkv + kvh) * page_size + key % page_size;
+        const A* kp = k_cache + base * hd;
         float dot = 0.f;
-        for (int d = 0; d < hd; d += Vec16<A>::N) {
-          float kv[Vec16<A>::N];
-          Vec16<A>::load(kp + d, kv);
+        if (vec) {
+          for (int d = 0; d < hd; d += Vec16<A>::N) {
+            float kv[Vec16<A>::N];
+            Vec16<A>::load(kp + d, kv);
 #pragma unroll
-          for (int i = 0; i < Vec16<A>::N; ++i) dot += qs[d + i] * kv[i];
+            for (int i = 0; i < Vec16<A>::N; ++i) dot += qs[d + i] * kv[i];
+          }
+        } else {
+          for (int d = 0; d < hd; ++d) dot += qs[d] * qb_to_float<A>(kp[d]);
         }
         s = dot * scale;
       }
@@ -97,38 +103,39 @@ __global__ void paged_attention_simt_kernel(
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long bj = __shfl_sync(0xffffffffu, base, j);
       if (bj < 0) continue;
-      const A* vp = v_cache + bj;
+      const A* vp = v_cache + bj * vd;
 #pragma unroll
       for (int i = 0; i < ATT_MAX_HD / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] += pj * qb_to_float<A>(vp[d]);
+        if (d < vd) acc[i] += pj * qb_to_float<A>(vp[d]);
       }
     }
     m = m_new;
   }
-  A* orow = out + ((size_t)t * nq + h) * hd;
+  A* orow = out + ((size_t)t * nq + h) * vd;
   const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < ATT_MAX_HD / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) orow[d] = qb_from_float<A>(acc[i] * inv_l);
+    if (d < vd) orow[d] = qb_from_float<A>(acc[i] * inv_l);
   }
 }
 
 extern "C" int qb_paged_attention_simt(const void* q, int dtype, const void* k_cache, const void* v_cache,
                                        void* out, const int* tok_pos, const int* tok_req,
                                        const int* block_table, int bt_stride, int T, int nq, int nkv, int hd,
-                                       int page_size, int num_pages, float scale, int window, int* status,
+                                       int vd, int page_size, int num_pages, float scale, int window, int* status,
                                        cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd % 16 || hd > ATT_MAX_HD || nq % nkv || page_size <= 0) return QB_ERR_UNSUPPORTED;
+  if (hd <= 0 || vd <= 0 || hd > ATT_MAX_HD || vd > ATT_MAX_HD || nq % nkv || page_size <= 0) return QB_ERR_UNSUPPORTED;
+  const int vec = (hd % 8 == 0 && ((uintptr_t)k_cache & 15) == 0) ? 1 : 0;      // key rows start on 16 bytes
   const long warps = (long)T * nq;
   const int blocks = (int)((warps + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = (size_t)ATT_WARPS * hd * sizeof(float);
   QB_DISPATCH_DTYPE(dtype, A,
                     paged_attention_simt_kernel<A><<<blocks, ATT_WARPS * 32, smem, stream>>>(
                         (const A*)q, (const A*)k_cache, (const A*)v_cache, (A*)out, tok_pos, tok_req,
-                        block_table, bt_stride, T, nq, nkv, hd, page_size, num_pages, scale, window, status));
+                        block_table, bt_stride, T, nq, nkv, hd, vd, page_size, num_pages, scale, window, vec, status));
   QB_LAUNCH_CHECK();
   return 0;
 }

@@ -36,6 +36,7 @@ UNITS = {
     "experts": ["moe.cu", "router_gemm_mma.cu", "expert_gemm_tc.cu"],
     "recurrent": ["short_conv.cu", "delta_rule.cu"],
     "latent": ["latent_attention.cu"],
+    "linear_attention": ["gla.cu"],
 }
 
 

@@ -15,8 +15,7 @@
 // barrier.  One token (decoding) or a portion of a prompt is the same code, and a column's numbers do not
 // depend on which block owns it, so a position's numbers depend neither on the cut nor on the batch.
 //
-// A second kernel divides each head's o by its root mean square, multiplies by the gain and by
-// sigmoid(gate) and writes the activation dtype for the output projection.
+// The per-head RMS norm with gain and gate that follows is a kernel of the common unit (norm_embed.cu).
 #include "common.cuh"
 
 constexpr int DR_LANES = 8;   // lanes that share a column
@@ -188,40 +187,6 @@ extern "C" int qb_delta_rule(const float* proj, int proj_stride, int r_off, int 
   else if (rpt == 16) DR_LAUNCH(16);
   else DR_LAUNCH(32);
 #undef DR_LAUNCH
-  QB_LAUNCH_CHECK();
-  return 0;
-}
-
-// out[t, h*D + i] = o[t,h,i] / sqrt(mean_i(o[t,h,:]^2) + eps) * gain[h*D + i] * sigmoid(gate[t, h*D + i])
-// One warp a (token, head); the sum is a warp reduction in a fixed order.
-template <typename O>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate,
-                                      int gate_stride, const float* __restrict__ gain, O* __restrict__ out,
-                                      int T, int H, int D, float eps) {
-  const int lane = threadIdx.x & 31;
-  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wid >= (long)T * H) return;
-  const int t = (int)(wid / H), h = (int)(wid % H);
-  const float* row = o + ((size_t)t * H + h) * D;
-  float ss = 0.f;
-  for (int i = lane; i < D; i += 32) ss += row[i] * row[i];
-  ss = qb_warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss / (float)D + eps);
-  const float* g = gate + (size_t)t * gate_stride + (size_t)h * D;
-  for (int i = lane; i < D; i += 32) {
-    const float sg = 1.f / (1.f + expf(-g[i]));
-    out[((size_t)t * H + h) * D + i] = qb_from_float<O>(row[i] * inv * gain[h * D + i] * sg);
-  }
-}
-
-extern "C" int qb_head_norm_gate(const float* o, const float* gate, int gate_stride, const float* gain,
-                                 void* out, int out_dtype, int T, int H, int D, float eps,
-                                 cudaStream_t stream) {
-  if (T <= 0) return 0;
-  const long warps = (long)T * H;
-  const int blocks = (int)((warps + 3) / 4);
-  QB_DISPATCH_DTYPE(out_dtype, O, head_norm_gate_kernel<O><<<blocks, 128, 0, stream>>>(
-      o, gate, gate_stride, gain, (O*)out, T, H, D, eps));
   QB_LAUNCH_CHECK();
   return 0;
 }

@@ -12,7 +12,9 @@
 //              TMEM; tcgen05.commit frees the stage and, at the end, signals the epilogue.
 //   warps 2-5: epilogue (2-9 in the blocks of a pair).  tcgen05.ld (one TMEM lane = one output feature per thread), then
 //              MODE 1: act[p, j] = silu(gate) * up  (bfloat16),  gate/up = two accumulators;
-//              MODE 2: y[pair(p), n] = w[pair(p)] * acc  (float32).
+//              MODE 2: y[pair(p), n] = w[pair(p)] * acc  (float32);
+//              MODE 3: act[p, j] = relu(acc)^2  (bfloat16): the first product of ungated experts, whose weights
+//              are one matrix [E, I, K] (token rows fetched as in MODE 1, weight tiles laid out as in MODE 2).
 //   (src/quanta/minimax/moe.py:59-88; rows p sorted by expert, see the plan kernels.)
 //
 // The token rows are read in p order: MODE 1 reads a gathered copy of x (gather kernel below) as one box a
@@ -232,7 +234,7 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
   }
-  if (MODE == 1 && gather_k > 0) {
+  if (MODE != 2 && gather_k > 0) {
     // the token rows are fetched one by one from the step's activations: row i of the tile is the token
     // of the i-th pair of this expert
     for (int i = threadIdx.x; i < rows; i += blockDim.x) s_pair[i] = sorted_pair[row0 + i] / gather_k;
@@ -250,7 +252,7 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
     // weights are read once per step by tiles of few rows (evict first); the 256-row tiles of one expert run at
     // about the same time and read the same weights, so those stay (measured: 5 % on a 16,384-token step)
     const uint64_t pol_w = PAIR ? l2_policy_evict_last() : l2_policy_evict_first(), pol_x = l2_policy_evict_last();
-    const bool by_row = MODE == 1 && gather_k > 0;
+    const bool by_row = MODE != 2 && gather_k > 0;
     // the tile rows this block fetches: all of them, or a pair's half
     const int r_lo = PAIR ? (int)rank * (n_mma / 2) : 0;
     const int r_hi = PAIR ? min(rows, r_lo + n_mma / 2) : rows;
@@ -386,6 +388,19 @@ expert_gemm_tc_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
             for (int i = 0; i < 16; ++i)
               if (c0 + i < rows) dst[(size_t)i * N_out] = r[i];
           }
+        } else if (MODE == 3) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)(row0 + c0) * N_out;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (c0 + i < rows) {
+              const float a = fmaxf(__uint_as_float(v0[i]), 0.f);
+              if (feat < N_out) dst[(size_t)i * N_out + feat] = __float2bfloat16_rn(a * a);
+              if (NM == 2 && feat + EG_M < N_out) {
+                const float b = fmaxf(__uint_as_float(v1[i]), 0.f);
+                dst[(size_t)i * N_out + feat + EG_M] = __float2bfloat16_rn(b * b);
+              }
+            }
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -495,7 +510,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
                                  int* status, cudaStream_t stream) {
   if (max_tiles <= 0 || n_pairs <= 0) return 0;
   if (K % 8 || K <= 0 || N_out <= 0 || NT < 16 || NT > 256 || NT % 16 || max_tiles > 65535) return QB_ERR_UNSUPPORTED;
-  if (mode != 1 && mode != 2) return QB_ERR_BAD_ARG;
+  if (mode != 1 && mode != 2 && mode != 3) return QB_ERR_BAD_ARG;
   // weight tiles a block: gate and up (mode 1); two blocks of 128 features for the down product of 256-row
   // token tiles (see the kernel)
   const int nm = (mode == 1 || NT >= 128) ? 2 : 1;
@@ -506,7 +521,7 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
   CUtensorMap tm_w, tm_x;
   int rc = make_map(&tm_w, weights, (uint64_t)E * (mode == 1 ? 2 : 1) * N_out, (uint64_t)K, EG_M);
   if (rc) return rc;
-  if (gather_k < 0 || (gather_k > 0 && (mode != 1 || n_rows <= 0))) return QB_ERR_BAD_ARG;
+  if (gather_k < 0 || (gather_k > 0 && (mode == 2 || n_rows <= 0))) return QB_ERR_BAD_ARG;
   rc = gather_k > 0 ? make_map(&tm_x, x_rows, (uint64_t)n_rows, (uint64_t)K, 1u)
                     : make_map(&tm_x, x_rows, (uint64_t)n_pairs, (uint64_t)K, (uint32_t)(pair ? NT / 2 : NT));
   if (rc) return rc;
@@ -550,8 +565,11 @@ extern "C" int qb_expert_gemm_tc(int mode, const void* x_rows, const void* weigh
                                                N_out, NT, stages, tmem_cols, GK, status);                          \
   } while (0)
   if (pair && mode == 1) QB_EG(expert_gemm_tc_pair_kernel<1>, gather_k, EG_PAIR_THREADS);
+  else if (pair && mode == 3) QB_EG(expert_gemm_tc_pair_kernel<3>, gather_k, EG_PAIR_THREADS);
   else if (pair) QB_EG(expert_gemm_tc_pair_kernel<2>, 0, EG_PAIR_THREADS);
   else if (mode == 1) QB_EG((expert_gemm_tc_kernel<1, 2>), gather_k, EG_THREADS);
+  else if (mode == 3 && nm == 2) QB_EG((expert_gemm_tc_kernel<3, 2>), gather_k, EG_THREADS);
+  else if (mode == 3) QB_EG((expert_gemm_tc_kernel<3, 1>), gather_k, EG_THREADS);
   else if (nm == 2) QB_EG((expert_gemm_tc_kernel<2, 2>), 0, EG_THREADS);
   else QB_EG((expert_gemm_tc_kernel<2, 1>), 0, EG_THREADS);
 #undef QB_EG

@@ -5,9 +5,17 @@
 //   scores = sigmoid(logits); choice = scores + bias (selection only); top-k by (choice desc, expert
 //   asc); w = scores[idx]; w /= sum(w) + 1e-20 if renorm and k > 1; w *= scale
 //   (src/quanta/minimax/moe.py:36-56).
+//   A second way of weighting (`renorm` = QB_ROUTE_SOFTMAX_CHOSEN): choice = logits + bias, top-k by the
+//   same order, w = softmax over the chosen values only, times scale.
 //   expert e on row x: down_e( silu(gate_e x) * up_e x ), times w, summed over the k slots in slot
-//   order by the next norm kernel (src/quanta/minimax/moe.py:59-88).
+//   order by the next norm kernel (src/quanta/minimax/moe.py:59-88); or, ungated (MODE 3 below),
+//   down_e( relu(up_e x)^2 ).
 #include "common.cuh"
+
+// values of the `renorm` argument of the routing kernels: how the chosen experts are weighted
+#define QB_ROUTE_SIGMOID_RAW 0        // sigmoid scores as they are
+#define QB_ROUTE_SIGMOID_RENORM 1     // sigmoid scores divided by their sum
+#define QB_ROUTE_SOFTMAX_CHOSEN 2     // choice by logit + bias; softmax over the chosen values
 
 // ---------------------------------------------------------------------------------------------
 // routing: one warp per token
@@ -40,15 +48,19 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
     score[i] = 0.f;
     if (e < E) {
       const float x = logit[i];
-      const float s = 1.f / (1.f + expf(-x));
-      score[i] = s;
-      choice[i] = s + bias[i];
+      if (renorm == QB_ROUTE_SOFTMAX_CHOSEN) {
+        score[i] = choice[i] = x + bias[i];
+      } else {
+        const float s = 1.f / (1.f + expf(-x));
+        score[i] = s;
+        choice[i] = s + bias[i];
+      }
     } else {
       choice[i] = -INFINITY;
       taken |= 1u << i;
     }
   }
-  float sum = 0.f;
+  float sum = 0.f, first = 0.f;
   for (int r = 0; r < k; ++r) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -74,7 +86,11 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
       for (int i = 0; i < NPL; ++i)
         if (i == (bi >> 5)) mine = score[i];
     }
-    const float sc = __shfl_sync(0xffffffffu, mine, bi & 31);     // the bias-free score of the chosen expert
+    float sc = __shfl_sync(0xffffffffu, mine, bi & 31);     // the bias-free score of the chosen expert
+    if (renorm == QB_ROUTE_SOFTMAX_CHOSEN) {                // the first chosen value is the largest
+      if (r == 0) first = sc;
+      sc = expf(sc - first);
+    }
     sum += sc;
     if (lane == 0) {
       idx_row[r] = bi;
@@ -83,7 +99,7 @@ __device__ __forceinline__ void select_topk(const float (&logit)[NPL], const flo
     }
   }
   __syncwarp();
-  const float denom = (renorm && k > 1) ? sum + 1e-20f : 1.f;
+  const float denom = renorm == QB_ROUTE_SOFTMAX_CHOSEN ? sum : (renorm && k > 1) ? sum + 1e-20f : 1.f;
   for (int r = lane; r < k; r += 32) w_row[r] = s_score[r] / denom * scale;
 }
 
@@ -618,6 +634,7 @@ extern "C" int qb_moe_plan(const int* idx, int n_pairs, int E, int BM, int* plan
 // grouped products, SIMT.  Tile = 32 sorted rows of one expert x 64 output features, k slices of 16.
 //   MODE 1: act[p, j]   = silu(x[tok(p)] . W13[e][j]) * (x[tok(p)] . W13[e][I + j]),  j < I
 //   MODE 2: y[pair(p), n] = w[pair(p)] * (act[p] . W2[e][n]),  n < H
+//   MODE 3: act[p, j]   = relu(x[tok(p)] . W1[e][j])^2,  j < I            (ungated experts; weights [E, I, K])
 // Each output is one sequential float32 sum over the inner dimension.
 // ---------------------------------------------------------------------------------------------
 constexpr int MG_BM = 32, MG_BN = 64, MG_BK = 16;
@@ -628,7 +645,8 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
                                         const float* __restrict__ pair_w, const int* __restrict__ plan,
                                         const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                                         int E, int top_k, int K, int N) {
-  // MODE 1: K = hidden, N = I (weights [E, 2N, K]); MODE 2: K = I, N = hidden (weights [E, N, K])
+  // MODE 1: K = hidden, N = I (weights [E, 2N, K]); MODE 2: K = I, N = hidden (weights [E, N, K]);
+  // MODE 3: K = hidden, N = I (weights [E, N, K])
   const int* offsets = plan + 2 * E;
   const int num_tiles = plan[3 * E + 1];
   const int tile = blockIdx.y;
@@ -644,7 +662,7 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
   if (tid < MG_BM) {
     const int p = row0 + tid;
     int r = -1;
-    if (p < row_end) r = (MODE == 1) ? sorted_pair[p] / top_k : p;
+    if (p < row_end) r = (MODE != 2) ? sorted_pair[p] / top_k : p;
     src_row[tid] = r;
   }
   __syncthreads();
@@ -712,6 +730,13 @@ __global__ void moe_grouped_simt_kernel(const X* __restrict__ x, const W* __rest
         const float g = acc[0][i][j], u = acc[MODE == 1 ? 1 : 0][i][j];
         out[(size_t)p * N + gn] = qb_from_float<O>(g / (1.f + expf(-g)) * u);
       }
+    } else if (MODE == 3) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int gn = n0 + tx * 4 + j;
+        const float u = fmaxf(acc[0][i][j], 0.f);
+        if (gn < N) out[(size_t)p * N + gn] = qb_from_float<O>(u * u);
+      }
     } else {
       const int pair = sorted_pair[p];
       const float w = pair_w[pair];
@@ -739,6 +764,10 @@ extern "C" int qb_moe_grouped_simt(int mode, const void* x, int x_dtype, const v
           top_k, K, N);
     else if (mode == 2)
       moe_grouped_simt_kernel<X, W, O, 2><<<grid, 256, 0, stream>>>(
+          (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
+          top_k, K, N);
+    else if (mode == 3)
+      moe_grouped_simt_kernel<X, W, O, 3><<<grid, 256, 0, stream>>>(
           (const X*)x, (const W*)weights, (O*)out, sorted_pair, pair_w, plan, tile_expert, tile_row0, E,
           top_k, K, N);
     else

@@ -7,39 +7,62 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// h[t,:] = float(table[ids[t],:]) * scale     (reference: src/quanta/minimax/model.py:91)
+// h[t,c,:] = float(table[ids[t],:]) * scale (+ float(pos_table[tok_pos[t],:]))   for every copy c
+// (reference: src/quanta/minimax/model.py:91).  pos_table: a learned vector per position (not scaled), null for
+// none; copies: how many equal residual streams the model keeps (1 for the usual single stream).
 // ---------------------------------------------------------------------------------------------
 template <typename W>
 __global__ void embedding_kernel(float* __restrict__ h, const W* __restrict__ table,
-                                 const int* __restrict__ ids, int T, int H, int V, float scale, int* status) {
+                                 const int* __restrict__ ids, int T, int H, int V, float scale,
+                                 const W* __restrict__ pos_table, const int* __restrict__ tok_pos, int n_pos,
+                                 int copies, int* status) {
   const int t = blockIdx.x;
   if (t >= T) return;
   const int id = ids[t];
-  float* out = h + (size_t)t * H;
-  if (id < 0 || id >= V) {
-    if (threadIdx.x == 0) qb_set_status(status, QB_STATUS_BAD_TOKEN, id, 1);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = 0.f;
+  float* out = h + (size_t)t * copies * H;
+  const int p = pos_table != nullptr ? tok_pos[t] : 0;
+  const bool bad_id = id < 0 || id >= V, bad_pos = pos_table != nullptr && (p < 0 || p >= n_pos);
+  if (bad_id || bad_pos) {
+    if (threadIdx.x == 0) {
+      if (bad_id) qb_set_status(status, QB_STATUS_BAD_TOKEN, id, 1);
+      else qb_set_status(status, QB_STATUS_BAD_POSITION, p, 1);
+    }
+    for (int i = threadIdx.x; i < copies * H; i += blockDim.x) out[i] = 0.f;
     return;
   }
   const W* row = table + (size_t)id * H;
+  const W* prow = pos_table != nullptr ? pos_table + (size_t)p * H : nullptr;
   if (H % 8 == 0) {
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       float v[8];
       QbVec8<W>::load(row + i, v);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] *= scale;
-      QbVec8<float>::store(out + i, v);
+      if (prow != nullptr) {
+        float pv[8];
+        QbVec8<W>::load(prow + i, pv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += pv[e];
+      }
+      for (int c = 0; c < copies; ++c) QbVec8<float>::store(out + (size_t)c * H + i, v);
     }
   } else {
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = qb_to_float<W>(row[i]) * scale;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = qb_to_float<W>(row[i]) * scale;
+      if (prow != nullptr) v += qb_to_float<W>(prow[i]);
+      for (int c = 0; c < copies; ++c) out[(size_t)c * H + i] = v;
+    }
   }
 }
 
 extern "C" int qb_embedding(float* h, const void* table, int table_dtype, const int* ids, int T, int H,
-                            int V, float scale, int* status, cudaStream_t stream) {
+                            int V, float scale, const void* pos_table, const int* tok_pos, int n_pos, int copies,
+                            int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (copies < 1 || (pos_table != nullptr && (tok_pos == nullptr || n_pos <= 0))) return QB_ERR_BAD_ARG;
   QB_DISPATCH_DTYPE(table_dtype, W,
-                    embedding_kernel<W><<<T, 256, 0, stream>>>(h, (const W*)table, ids, T, H, V, scale, status));
+                    embedding_kernel<W><<<T, 256, 0, stream>>>(h, (const W*)table, ids, T, H, V, scale,
+                                                               (const W*)pos_table, tok_pos, n_pos, copies, status));
   QB_LAUNCH_CHECK();
   return 0;
 }
@@ -222,6 +245,178 @@ extern "C" int qb_silu_mul(const void* gu, void* out, int dtype, int n_rows, int
   const size_t n = (size_t)n_rows * I;
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   QB_DISPATCH_DTYPE(dtype, A, silu_mul_kernel<A><<<blocks, 256, 0, stream>>>((const A*)gu, (A*)out, n_rows, I));
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Several residual streams per token (x [T, S, H] float32), read by each sublayer as a weighted sum and written
+// back through a mixing matrix.  One launch does what lies between two sublayers: the write-back of the
+// sublayer that has just run, the read of the next one, and its RMS norm.  Row r (token rows[r] or r):
+//   y      = sum_k delta[tok, k, :]                               (the sublayer's output, slots in order; may be null)
+//   x'_t   = sum_s mix[s, t] * x_s + mult * out_w[t] * y          (all streams from the old ones; skipped without delta)
+//   if store: x[tok] = x'
+//   u      = sum_t read_w[t] * x'_t                               (read_w null: the plain sum of the streams)
+//   out[r] = w * (u * rsqrt(mean(u^2) + eps))                     (out null: only the write-back; w null: u itself)
+// Everything is float32 and every sum has a fixed order, so a row's numbers never depend on the batch.
+// ---------------------------------------------------------------------------------------------
+constexpr int QB_MAX_STREAMS = 16;
+
+template <typename D, typename O>
+__global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, int S, const D* __restrict__ delta, int K,
+                                           const float* __restrict__ mix, const float* __restrict__ out_w, float mult,
+                                           const float* __restrict__ read_w, const float* __restrict__ w,
+                                           O* __restrict__ out, const int* __restrict__ rows, int n_rows, int H,
+                                           float eps, int store) {
+  extern __shared__ float sm_u[];          // H floats (u) + 32 scratch
+  float* scratch = sm_u + H;
+  __shared__ float s_mix[QB_MAX_STREAMS * QB_MAX_STREAMS], s_out[QB_MAX_STREAMS], s_read[QB_MAX_STREAMS];
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const int tok = rows ? rows[r] : r;
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[i] = mix ? mix[i] : 0.f;
+  for (int i = threadIdx.x; i < S; i += blockDim.x) {
+    s_out[i] = out_w ? mult * out_w[i] : 0.f;
+    s_read[i] = read_w ? read_w[i] : 1.f;
+  }
+  __syncthreads();
+  float* xrow = x + (size_t)tok * S * H;
+  const D* drow = delta ? delta + (size_t)tok * K * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float xs[QB_MAX_STREAMS];
+    for (int s = 0; s < S; ++s) xs[s] = xrow[(size_t)s * H + i];
+    float u = 0.f;
+    if (drow != nullptr) {
+      float y = 0.f;
+      for (int k = 0; k < K; ++k) y += qb_to_float<D>(drow[(size_t)k * H + i]);
+      for (int t = 0; t < S; ++t) {
+        float v = 0.f;
+        for (int s = 0; s < S; ++s) v = fmaf(s_mix[s * S + t], xs[s], v);
+        v = fmaf(s_out[t], y, v);
+        if (store) xrow[(size_t)t * H + i] = v;
+        u = fmaf(s_read[t], v, u);
+      }
+    } else {
+      for (int t = 0; t < S; ++t) u = fmaf(s_read[t], xs[t], u);
+    }
+    sm_u[i] = u;
+    ss += u * u;
+  }
+  if (out == nullptr) return;
+  const float total = qb_block_sum(ss, scratch);
+  const float r_inv = w != nullptr ? rsqrtf(total / (float)H + eps) : 1.f;
+  O* orow = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    orow[i] = qb_from_float<O>(w != nullptr ? w[i] * (sm_u[i] * r_inv) : sm_u[i]);
+}
+
+extern "C" int qb_streams_mix_rmsnorm(float* x, int S, const void* delta, int delta_dtype, int K, const float* mix,
+                                      const float* out_w, float mult, const float* read_w, const float* w, void* out,
+                                      int out_dtype, const int* rows, int n_rows, int H, float eps, int store,
+                                      cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (S < 1 || S > QB_MAX_STREAMS) return QB_ERR_UNSUPPORTED;
+  if (delta != nullptr && (mix == nullptr || out_w == nullptr || K < 1)) return QB_ERR_BAD_ARG;
+  const size_t smem = (size_t)(H + 32) * sizeof(float);
+  if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
+  const int threads = H >= 2048 ? 512 : 256;
+  QB_DISPATCH_DTYPE(delta_dtype, D, QB_DISPATCH_DTYPE(out_dtype, O, {
+    auto kern = streams_mix_rmsnorm_kernel<D, O>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<n_rows, threads, smem, stream>>>(x, S, (const D*)delta, K, mix, out_w, mult, read_w, w, (O*)out, rows,
+                                            n_rows, H, eps, store);
+  }));
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[r, c] = relu(x[r, c])^2     (the activation of an ungated feed-forward; float32 inside)
+// ---------------------------------------------------------------------------------------------
+template <typename A>
+__global__ void relu_squared_kernel(const A* __restrict__ x, A* __restrict__ out, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(qb_to_float<A>(x[i]), 0.f);
+    out[i] = qb_from_float<A>(v * v);
+  }
+}
+
+extern "C" int qb_relu_squared(const void* x, void* out, int dtype, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  QB_DISPATCH_DTYPE(dtype, A, relu_squared_kernel<A><<<blocks, 256, 0, stream>>>((const A*)x, (A*)out, (size_t)n));
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-head RMS norm with a gain and an elementwise gate, for mixers whose heads are normed before the output
+// projection:  out[t, h*D + i] = o[t,h,i] / sqrt(mean_i(o[t,h,:]^2) + eps) * gain[..] * act(gate[t, h*D + i])
+// gain: [H*D] (gain_shared 0) or [D], the same for every head (gain_shared 1); act: sigmoid (gate_kind 0) or
+// silu (gate_kind 1).  One warp a (token, head); the sum is a warp reduction in a fixed order.
+// ---------------------------------------------------------------------------------------------
+template <typename O>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                      int gate_stride, const float* __restrict__ gain, O* __restrict__ out,
+                                      int T, int H, int D, float eps, int gain_shared, int gate_kind) {
+  const int lane = threadIdx.x & 31;
+  const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (long)T * H) return;
+  const int t = (int)(wid / H), h = (int)(wid % H);
+  const float* row = o + ((size_t)t * H + h) * D;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) ss += row[i] * row[i];
+  ss = qb_warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)D + eps);
+  const float* g = gate + (size_t)t * gate_stride + (size_t)h * D;
+  const float* gn = gain + (gain_shared ? 0 : h * D);
+  for (int i = lane; i < D; i += 32) {
+    const float sg = 1.f / (1.f + expf(-g[i]));
+    const float a = gate_kind == 1 ? g[i] * sg : sg;
+    out[((size_t)t * H + h) * D + i] = qb_from_float<O>(row[i] * inv * gn[i] * a);
+  }
+}
+
+extern "C" int qb_head_norm_gate(const float* o, const float* gate, int gate_stride, const float* gain,
+                                 void* out, int out_dtype, int T, int H, int D, float eps, int gain_shared,
+                                 int gate_kind, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (gate_kind != 0 && gate_kind != 1) return QB_ERR_BAD_ARG;
+  const long warps = (long)T * H;
+  const int blocks = (int)((warps + 3) / 4);
+  QB_DISPATCH_DTYPE(out_dtype, O, head_norm_gate_kernel<O><<<blocks, 128, 0, stream>>>(
+      o, gate, gate_stride, gain, (O*)out, T, H, D, eps, gain_shared, gate_kind));
+  QB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One gate per (token, head): x[t, h, :] *= sigmoid(gate[t, h]) in place (float32 inside, one rounding).
+// gate: rows of gate_stride elements of the activation dtype (columns of a wider fused projection).
+// ---------------------------------------------------------------------------------------------
+template <typename A>
+__global__ void head_sigmoid_gate_kernel(A* __restrict__ x, const A* __restrict__ gate, int gate_stride, int T,
+                                         int H, int D) {
+  const size_t n = (size_t)T * H * D;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t th = i / D, t = th / H, h = th % H;
+    const float g = qb_to_float<A>(gate[t * gate_stride + h]);
+    x[i] = qb_from_float<A>(qb_to_float<A>(x[i]) / (1.f + expf(-g)));
+  }
+}
+
+extern "C" int qb_head_sigmoid_gate(void* x, const void* gate, int gate_stride, int dtype, int T, int H, int D,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const size_t n = (size_t)T * H * D;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  QB_DISPATCH_DTYPE(dtype, A, head_sigmoid_gate_kernel<A><<<blocks, 256, 0, stream>>>((A*)x, (const A*)gate,
+                                                                                      gate_stride, T, H, D));
   QB_LAUNCH_CHECK();
   return 0;
 }

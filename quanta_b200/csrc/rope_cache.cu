@@ -1,11 +1,16 @@
-// q/k RMSNorm + partial rotary position encoding + write of K and V into the paged cache, one kernel.
+// q/k RMSNorm + partial rotary position encoding + query temperature + write of K and V into the paged cache,
+// one kernel.
 //
-// Input is the fused projection row [q | k | v] of every token of the step.  For each token:
+// Input is a row of a fused projection, [q | k | v | anything else] (row_stride elements), of every token of the
+// step; a layer that reads another layer's cache has rows [q | anything else] (has_kv = 0).  For each token:
 //   q, k  <- RMSNorm (none | over all heads of the row | per head), float32
 //            (src/quanta/minimax/model_m3.py:15-17 / src/quanta/minimax/attention.py:172-182)
 //   q, k  <- rotate-half on the first `rd` dims of each head, pair j using position axis
 //            pair_axis[j] and angle float(pos) * inv_freq[j]  (src/quanta/minimax/model_m3.py:83-96)
-//   q     -> q_out [T, nq, hd];  k, v -> cache pages [page, kv_head, slot, hd] through the block table
+//   q     <- q * (1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1))     (temp_every > 0: a query
+//            temperature that grows with the position, float32)
+//   q     -> q_out [T, nq, hd];  k -> pages [page, kv_head, slot, hd], v -> pages [page, kv_head, slot, vd]
+//            through the block table (keys and values may have different head sizes)
 // One rounding to the activation dtype, at the store.  One block per token.
 #include "common.cuh"
 
@@ -15,43 +20,47 @@
 
 template <typename A>
 __global__ void qknorm_rope_write_kernel(
-    const A* __restrict__ qkv, A* __restrict__ q_out, A* __restrict__ k_cache, A* __restrict__ v_cache,
+    const A* __restrict__ qkv, int row_stride, A* __restrict__ q_out, A* __restrict__ k_cache, A* __restrict__ v_cache,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, int norm_kind, float eps,
     const float* __restrict__ inv_freq, const int* __restrict__ pair_axis,
     const int* __restrict__ positions, int n_axes, const int* __restrict__ tok_pos,
     const int* __restrict__ tok_req, const int* __restrict__ block_table, int bt_stride, int T, int nq,
-    int nkv, int hd, int rd, int page_size, int num_pages, int* status) {
+    int nkv_all, int hd, int vd, int has_kv, int rd, float temp_coef, int temp_every, int page_size, int num_pages,
+    int vec, int* status) {
   extern __shared__ float smem[];
   const int t = blockIdx.x;
   if (t >= T) return;
-  const int qn = nq * hd, kn = nkv * hd;
+  const int nkv = has_kv ? nkv_all : 0;
+  const int qn = nq * hd, kn = nkv * hd, vn = nkv * vd;
   float* buf = smem;                 // [qn + kn]  q then k
   float* cs = buf + qn + kn;         // [rd/2] cos, [rd/2] sin
   float* scratch = cs + rd;          // 32 + (nq + nkv) head statistics
   float* head_r = scratch + 32;
-  const A* row = qkv + (size_t)t * (qn + 2 * kn);
+  const A* row = qkv + (size_t)t * row_stride;
   const int half = rd / 2;
   // Where this token's K and V go is a chain of three dependent loads (position, request, page id), and the
   // norm gains come from memory that the layer's expert weights have pushed out of L2: both are asked for
   // now, so that their latency passes under the phases below instead of after them.
   int pos = 0, page = -1;
-  if (k_cache != nullptr) {
-    pos = tok_pos[t];
-    page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
-  }
-  const int n_chunks = (qn + kn) / 8;
+  if (k_cache != nullptr || temp_every > 0) pos = tok_pos[t];
+  if (k_cache != nullptr) page = block_table[(size_t)tok_req[t] * bt_stride + pos / page_size];
+  const int n_chunks = vec ? (qn + kn) / 8 : 0;
   float w_first[8];                  // the gains of this thread's first chunk (NORM_PER_LAYER)
   if (norm_kind == NORM_PER_LAYER && (int)threadIdx.x < n_chunks) {
     const int i = threadIdx.x * 8;
     QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w_first);
   }
 
-  // 16-byte loads, all of a thread's loads issued before their first use
+  if (vec) {
+    // 16-byte loads, all of a thread's loads issued before their first use
 #pragma unroll 4
-  for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
-    float v[8];
-    QbVec8<A>::load(row + c * 8, v);
-    QbVec8<float>::store(buf + c * 8, v);
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+      float v[8];
+      QbVec8<A>::load(row + c * 8, v);
+      QbVec8<float>::store(buf + c * 8, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < qn + kn; i += blockDim.x) buf[i] = qb_to_float<A>(row[i]);
   }
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
     const int ax = pair_axis ? pair_axis[j] : 0;
@@ -76,22 +85,27 @@ __global__ void qknorm_rope_write_kernel(
     float tq = 0.f, tk = 0.f;
     for (int h = 0; h < nq; ++h) tq += head_r[h];
     for (int h = 0; h < nkv; ++h) tk += head_r[nq + h];
-    const float rq = rsqrtf(tq / (float)qn + eps), rk = rsqrtf(tk / (float)kn + eps);
+    const float rq = rsqrtf(tq / (float)qn + eps), rk = rsqrtf(tk / (float)max(kn, 1) + eps);
+    if (vec) {
 #pragma unroll 4
-    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
-      const int i = c * 8;
-      float w[8], v[8];
-      if (c == (int)threadIdx.x) {
+      for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+        const int i = c * 8;
+        float w[8], v[8];
+        if (c == (int)threadIdx.x) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) w[e] = w_first[e];
-      } else {
-        QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w);
+          for (int e = 0; e < 8; ++e) w[e] = w_first[e];
+        } else {
+          QbVec8<float>::load(i < qn ? q_norm_w + i : k_norm_w + (i - qn), w);
+        }
+        QbVec8<float>::load(buf + i, v);
+        const float r = i < qn ? rq : rk;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = w[e] * (v[e] * r);
+        QbVec8<float>::store(buf + i, v);
       }
-      QbVec8<float>::load(buf + i, v);
-      const float r = i < qn ? rq : rk;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = w[e] * (v[e] * r);
-      QbVec8<float>::store(buf + i, v);
+    } else {
+      for (int i = threadIdx.x; i < qn + kn; i += blockDim.x)
+        buf[i] = (i < qn ? q_norm_w[i] : k_norm_w[i - qn]) * (buf[i] * (i < qn ? rq : rk));
     }
     __syncthreads();
   } else if (norm_kind == NORM_PER_HEAD) {
@@ -119,13 +133,20 @@ __global__ void qknorm_rope_write_kernel(
     buf[h * hd + j] = a * c - b * s;
     buf[h * hd + half + j] = b * c + a * s;
   }
-  __syncthreads();
+  if (half > 0) __syncthreads();
 
+  const float temp = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
   A* qo = q_out + (size_t)t * qn;
-  for (int c = threadIdx.x; c < qn / 8; c += blockDim.x) {
-    float v[8];
-    QbVec8<float>::load(buf + c * 8, v);
-    QbVec8<A>::store(qo + c * 8, v);
+  if (vec) {
+    for (int c = threadIdx.x; c < qn / 8; c += blockDim.x) {
+      float v[8];
+      QbVec8<float>::load(buf + c * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= temp;
+      QbVec8<A>::store(qo + c * 8, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) qo[i] = qb_from_float<A>(buf[i] * temp);
   }
 
   if (k_cache == nullptr) return;
@@ -135,28 +156,42 @@ __global__ void qknorm_rope_write_kernel(
   }
   const int slot = pos % page_size;
   const A* vrow = row + qn + kn;
-  for (int c = threadIdx.x; c < kn / 8; c += blockDim.x) {
-    const int i = c * 8, h = i / hd, d = i % hd;
-    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * hd + d;
-    float kv[8], vv[8];
-    QbVec8<float>::load(buf + qn + i, kv);
-    QbVec8<A>::load(vrow + i, vv);
-    QbVec8<A>::store(k_cache + dst, kv);
-    QbVec8<A>::store(v_cache + dst, vv);        // V passes through unchanged (the float round trip is exact)
+  if (vec) {
+    for (int c = threadIdx.x; c < kn / 8; c += blockDim.x) {
+      const int i = c * 8, h = i / hd, d = i % hd;
+      float kv[8];
+      QbVec8<float>::load(buf + qn + i, kv);
+      QbVec8<A>::store(k_cache + (((size_t)page * nkv + h) * page_size + slot) * hd + d, kv);
+    }
+    for (int c = threadIdx.x; c < vn / 8; c += blockDim.x) {
+      const int i = c * 8, h = i / vd, d = i % vd;
+      float vv[8];
+      QbVec8<A>::load(vrow + i, vv);
+      QbVec8<A>::store(v_cache + (((size_t)page * nkv + h) * page_size + slot) * vd + d, vv);   // V passes through unchanged
+    }
+  } else {
+    for (int i = threadIdx.x; i < kn; i += blockDim.x)
+      k_cache[(((size_t)page * nkv + i / hd) * page_size + slot) * hd + i % hd] = qb_from_float<A>(buf[qn + i]);
+    for (int i = threadIdx.x; i < vn; i += blockDim.x)
+      v_cache[(((size_t)page * nkv + i / vd) * page_size + slot) * vd + i % vd] = vrow[i];
   }
 }
 
 extern "C" int qb_qknorm_rope_write(
-    const void* qkv, int dtype, void* q_out, void* k_cache, void* v_cache, const float* q_norm_w,
+    const void* qkv, int dtype, int row_stride, void* q_out, void* k_cache, void* v_cache, const float* q_norm_w,
     const float* k_norm_w, int norm_kind, float eps, const float* inv_freq, const int* pair_axis,
     const int* positions, int n_axes, const int* tok_pos, const int* tok_req, const int* block_table,
-    int bt_stride, int T, int nq, int nkv, int hd, int rd, int page_size, int num_pages, int* status,
-    cudaStream_t stream) {
+    int bt_stride, int T, int nq, int nkv, int hd, int vd, int has_kv, int rd, float temp_coef, int temp_every,
+    int page_size, int num_pages, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (rd % 2 || rd > hd || rd < 0 || nq <= 0 || nkv <= 0 || page_size <= 0) return QB_ERR_BAD_ARG;
-  if (norm_kind != NORM_NONE && (q_norm_w == nullptr || k_norm_w == nullptr)) return QB_ERR_BAD_ARG;
-  if (hd % 8) return QB_ERR_UNSUPPORTED;        // rows are moved in 16-byte pieces
-  const size_t smem = (size_t)((nq + nkv) * hd + rd + 32 + nq + nkv) * sizeof(float);
+  if (rd % 2 || rd > hd || rd < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || hd <= 0 || vd <= 0) return QB_ERR_BAD_ARG;
+  if (norm_kind != NORM_NONE && (q_norm_w == nullptr || (has_kv && k_norm_w == nullptr))) return QB_ERR_BAD_ARG;
+  if (!has_kv && k_cache != nullptr) return QB_ERR_BAD_ARG;
+  const int nk = has_kv ? nkv : 0;
+  if (row_stride < nq * hd + nk * (hd + vd)) return QB_ERR_BAD_ARG;
+  // rows are moved in 16-byte pieces where every piece starts on such a boundary; else element by element
+  const int vec = (hd % 8 == 0 && vd % 8 == 0 && row_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0) ? 1 : 0;
+  const size_t smem = (size_t)((nq + nk) * hd + rd + 32 + nq + nk) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
   QB_DISPATCH_DTYPE(dtype, A, {
     auto kern = qknorm_rope_write_kernel<A>;
@@ -166,9 +201,10 @@ extern "C" int qb_qknorm_rope_write(
     }
     // steps of few tokens: more threads a token, so that each of the kernel's phases is short
     const int threads = T <= 64 ? 1024 : 256;
-    kern<<<T, threads, smem, stream>>>((const A*)qkv, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w, k_norm_w,
-                                   norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos, tok_req,
-                                   block_table, bt_stride, T, nq, nkv, hd, rd, page_size, num_pages, status);
+    kern<<<T, threads, smem, stream>>>((const A*)qkv, row_stride, (A*)q_out, (A*)k_cache, (A*)v_cache, q_norm_w,
+                                       k_norm_w, norm_kind, eps, inv_freq, pair_axis, positions, n_axes, tok_pos,
+                                       tok_req, block_table, bt_stride, T, nq, nkv, hd, vd, has_kv, rd, temp_coef,
+                                       temp_every, page_size, num_pages, vec, status);
   });
   QB_LAUNCH_CHECK();
   return 0;

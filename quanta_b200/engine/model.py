@@ -15,7 +15,7 @@ import torch
 from .. import kernels, matmul
 from ..config.registry import load_config
 from ..parts import block as _block  # noqa: F401  (registers the built-in block, embedding and head)
-from ..parts.base import CacheSpec, Part, TensorSpec, make
+from ..parts.base import CacheSpec, Part, StreamsPending, TensorSpec, make
 from ..parts.spec import ModelSpec
 from ..weights.loader import FolderSource, RandomSource, open_fetch
 from ..weights.safetensors_io import write_safetensors
@@ -34,6 +34,21 @@ def parse_dtype(d) -> torch.dtype:
 def _plain(pending):
     """A pending contribution as a tensor (one that is normed first is normed now)."""
     return pending.materialize() if hasattr(pending, "materialize") else pending
+
+
+def _stream_now(h, pending):
+    """The residual stream with the pending contribution added, as a new ``[T, hidden]`` float32 tensor (the sum
+    of the streams for a model that keeps several); ``h`` is left as it is."""
+    if h.dim() == 3 or isinstance(pending, StreamsPending):
+        x = h if h.dim() == 3 else h.unsqueeze(1)
+        out = torch.empty((x.shape[0], x.shape[2]), dtype=torch.float32, device=h.device)
+        y, mix, out_w, mult = (pending.y, pending.mix, pending.out_w, pending.mult) if pending is not None else (None, None, None, 0.0)
+        kernels.streams_mix_rmsnorm(x, y, mix, out_w, mult, None, None, 0.0, out, store=False)
+        return out
+    now = h.clone()
+    if pending is not None:
+        kernels.residual_add(now, _plain(pending))
+    return now
 
 
 def _walk(part: Part):
@@ -114,6 +129,8 @@ class Model:
         pending = None
         for pos, entry in enumerate(self.schedule):
             if entry.add_embedding:
+                if h.dim() == 3:
+                    raise NotImplementedError("adding the embedding again is not built for several residual streams")
                 # the stream so far, then the embedded tokens once more, both summed in float32
                 if pending is not None:
                     kernels.residual_add(h, _plain(pending))
@@ -121,10 +138,7 @@ class Model:
                 kernels.residual_add(h, embedded)
             pending = self.blocks[entry.layer].forward(h, pending, ctx, caches[pos], states[pos])
             if self.residual_trace is not None:
-                now = h.clone()
-                if pending is not None:
-                    kernels.residual_add(now, _plain(pending))
-                self.residual_trace.append(now)
+                self.residual_trace.append(_stream_now(h, pending))
         if want_rows is None or want_rows.numel() == 0:
             return None
         return self.head.forward(h, pending, want_rows, ctx)

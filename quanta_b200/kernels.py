@@ -22,7 +22,8 @@ NORM_NONE, NORM_PER_LAYER, NORM_PER_HEAD = 0, 1, 2
 _STATUS_TEXT = {1: "token id outside the vocabulary", 2: "page id outside the pool (block table)",
                 3: "expert id outside the expert table", 4: "a bounded device wait ran out",
                 5: "the decode attention scratch has too few entries per row",
-                6: "a request's state slot on the device is free or at another position than the host's record"}
+                6: "a request's state slot on the device is free or at another position than the host's record",
+                7: "a position beyond the table of learned position vectors"}
 _KERNEL_TEXT = {1: "embedding", 2: "rope/cache write", 3: "paged attention", 4: "expert plan",
                 5: "expert product", 6: "decode attention", 7: "prefill attention", 8: "state slots"}
 
@@ -98,15 +99,87 @@ def raise_on_status(status_host) -> None:
 
 # ------------------------------------------------------------------------------------------------
 def embedding(h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
-              scale: float = 1.0) -> None:
-    """``h[t] = float32(table[ids[t]]) * scale``."""
+              scale: float = 1.0, pos_table: torch.Tensor | None = None, tok_pos: torch.Tensor | None = None) -> None:
+    """``h[t] = float32(table[ids[t]]) * scale (+ float32(pos_table[tok_pos[t]]))``; ``h`` ``[T, H]``, or
+    ``[T, S, H]`` for a model with S residual streams, which all start as the same row."""
     _want(h, torch.float32, "h"); _want(ids, torch.int32, "ids")
-    T, H = h.shape
+    T, H = h.shape[0], h.shape[-1]
+    copies = h.shape[1] if h.dim() == 3 else 1
     V = table.shape[0]
     if table.shape[1] != H or ids.numel() != T:
         raise ValueError("embedding: shape mismatch")
-    _check(lib().qb_embedding(_p(h), _p(table), _code(table), _p(ids), T, H, V, ctypes.c_float(scale), _p(status),
+    n_pos = 0
+    if pos_table is not None:
+        _want(tok_pos, torch.int32, "tok_pos")
+        if pos_table.shape[1] != H or pos_table.dtype != table.dtype or tok_pos.numel() != T:
+            raise ValueError("embedding: the position table does not fit")
+        n_pos = pos_table.shape[0]
+    _check(lib().qb_embedding(_p(h), _p(table), _code(table), _p(ids), T, H, V, ctypes.c_float(scale), _p(pos_table),
+                              _p(tok_pos) if pos_table is not None else ctypes.c_void_p(0), n_pos, copies, _p(status),
                               _stream()), "embedding")
+
+
+MAX_STREAMS = 16
+
+
+def streams_mix_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, mix: torch.Tensor | None,
+                        out_w: torch.Tensor | None, mult: float, read_w: torch.Tensor | None,
+                        weight: torch.Tensor | None, eps: float, out: torch.Tensor | None,
+                        rows: torch.Tensor | None = None, store: bool = True) -> None:
+    """What lies between two sublayers of a model with several residual streams ``x`` ``[T, S, H]`` (float32), in
+    one launch: with ``delta`` (``[T, H]`` or ``[T, K, H]``, K partial results added in order) the write-back
+    ``x'_t = sum_s mix[s, t] x_s + mult * out_w[t] * delta`` (stored when ``store``); then the read
+    ``u = sum_t read_w[t] x'_t`` (``read_w`` None: the plain sum of the streams) and
+    ``out = weight * u * rsqrt(mean(u^2) + eps)`` (``weight`` None: ``u`` itself; ``out`` None: only the
+    write-back).  ``rows`` (int32) selects token rows; ``out`` then has one row per entry."""
+    _want(x, torch.float32, "x")
+    if x.dim() != 3 or x.shape[1] > MAX_STREAMS:
+        raise ValueError(f"streams_mix_rmsnorm: x must be [T, S, H] with S <= {MAX_STREAMS}")
+    T, S, H = x.shape
+    K = 1
+    if delta is not None:
+        K = delta.shape[1] if delta.dim() == 3 else 1
+        if delta.shape[0] != T or delta.shape[-1] != H:
+            raise ValueError("streams_mix_rmsnorm: delta shape mismatch")
+        _want(mix, torch.float32, "mix"); _want(out_w, torch.float32, "out_w")
+        if tuple(mix.shape) != (S, S) or out_w.numel() != S:
+            raise ValueError("streams_mix_rmsnorm: mix must be [S, S] and out_w [S]")
+    for t, n, size in ((read_w, "read_w", S), (weight, "weight", H)):
+        if t is not None:
+            _want(t, torch.float32, n)
+            if t.numel() != size:
+                raise ValueError(f"streams_mix_rmsnorm: {n} has {t.numel()} elements, expected {size}")
+    n = T if rows is None else rows.numel()
+    if rows is not None:
+        _want(rows, torch.int32, "rows")
+    if out is not None and (out.shape[0] != n or out.shape[1] != H):
+        raise ValueError("streams_mix_rmsnorm: out shape mismatch")
+    _check(lib().qb_streams_mix_rmsnorm(_p(x), S, _p(delta), _code(delta) if delta is not None else F32, K,
+                                        _p(mix) if delta is not None else ctypes.c_void_p(0),
+                                        _p(out_w) if delta is not None else ctypes.c_void_p(0), ctypes.c_float(mult),
+                                        _p(read_w), _p(weight), _p(out), _code(out) if out is not None else F32,
+                                        _p(rows), n, H, ctypes.c_float(eps), int(store), _stream()),
+           "streams_mix_rmsnorm")
+
+
+def relu_squared(x: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = relu(x)^2`` elementwise (float32 inside, one rounding)."""
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise ValueError("relu_squared: shape/dtype mismatch")
+    _check(lib().qb_relu_squared(_p(x), _p(out), _code(x), ctypes.c_longlong(x.numel()), _stream()), "relu_squared")
+
+
+def head_sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, n_heads: int, dim: int) -> None:
+    """``x[t, h, :] *= sigmoid(gate[t, h])`` in place; ``gate`` may be columns of a wider row-major matrix (its
+    row stride is honoured), in the dtype of ``x``."""
+    T = x.shape[0]
+    if x.numel() != T * n_heads * dim or gate.dtype != x.dtype or gate.shape[0] != T or gate.shape[1] != n_heads \
+            or gate.stride(1) != 1:
+        raise ValueError("head_sigmoid_gate: shape/dtype mismatch")
+    if not x.is_contiguous():
+        raise ValueError("head_sigmoid_gate: x must be contiguous")
+    _check(lib().qb_head_sigmoid_gate(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(gate.data_ptr()),
+                                      int(gate.stride(0)), _code(x), T, n_heads, dim, _stream()), "head_sigmoid_gate")
 
 
 def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -178,17 +251,27 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kind: int, eps: float,
                       inv_freq, pair_axis, positions, tok_pos, tok_req, block_table, nq: int, nkv: int,
-                      hd: int, rd: int, page_size: int, status) -> None:
+                      hd: int, rd: int, page_size: int, status, *, vd: int | None = None, has_kv: bool = True,
+                      q_temp_coef: float = 0.0, q_temp_every: int = 0) -> None:
+    """Rows ``[q | k | v | ...]`` of a fused projection (``qkv`` may be wider than the three; its row stride is
+    honoured) -> normed, rotated queries in ``q_out`` and keys / values in the pages.  ``vd``: the values' head
+    size when it differs from ``hd``; ``has_kv`` False: the rows start with q alone (a layer that reads another
+    layer's cache); ``q_temp_every`` > 0: q is multiplied by ``1 + q_temp_coef * ln(floor((pos + 1) /
+    q_temp_every) + 1)``."""
     T = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * hd:
+    vd = hd if vd is None else int(vd)
+    if qkv.stride(1) != 1 or qkv.shape[1] < nq * hd + (nkv * (hd + vd) if has_kv else 0):
         raise ValueError("qknorm_rope_write: qkv width mismatch")
     if q_out.dtype != qkv.dtype or q_out.numel() != T * nq * hd:
         raise ValueError("qknorm_rope_write: q_out mismatch")
     num_pages = 0
     if k_cache is not None:
+        if not has_kv:
+            raise ValueError("qknorm_rope_write: rows without keys and values cannot fill a cache")
         if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
             raise ValueError("qknorm_rope_write: cache dtype differs from activations")
-        if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
+        if (tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd)
+                or k_cache.shape[0] != v_cache.shape[0]):
             raise ValueError("qknorm_rope_write: cache shape mismatch")
         num_pages = k_cache.shape[0]
     _want(inv_freq, torch.float32, "inv_freq")
@@ -201,24 +284,27 @@ def qknorm_rope_write(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, norm_kin
         _want(pair_axis, torch.int32, "pair_axis")
     if norm_kind != NORM_NONE:
         want = (nq * hd, nkv * hd) if norm_kind == NORM_PER_LAYER else (hd, hd)
-        if q_norm_w.numel() != want[0] or k_norm_w.numel() != want[1]:
+        if q_norm_w.numel() != want[0] or (has_kv and k_norm_w.numel() != want[1]):
             raise ValueError("qknorm_rope_write: norm weight length does not fit the norm kind")
     _check(lib().qb_qknorm_rope_write(
-        _p(qkv), _code(qkv), _p(q_out), _p(k_cache), _p(v_cache), _p(q_norm_w), _p(k_norm_w), norm_kind,
+        ctypes.c_void_p(qkv.data_ptr()), _code(qkv), int(qkv.stride(0)), _p(q_out), _p(k_cache), _p(v_cache),
+        _p(q_norm_w), _p(k_norm_w) if has_kv else ctypes.c_void_p(0), norm_kind,
         ctypes.c_float(eps), _p(inv_freq), _p(pair_axis), _p(positions), n_axes, _p(tok_pos), _p(tok_req),
-        _p(block_table), block_table.shape[1], T, nq, nkv, hd, rd, page_size, num_pages, _p(status),
-        _stream()), "qknorm_rope_write")
+        _p(block_table), block_table.shape[1], T, nq, nkv, hd, vd, int(has_kv), rd, ctypes.c_float(q_temp_coef),
+        int(q_temp_every), page_size, num_pages, _p(status), _stream()), "qknorm_rope_write")
 
 
 def paged_attention_simt(q, k_cache, v_cache, out, tok_pos, tok_req, block_table, scale: float,
                          window: int, status) -> None:
     T, nq, hd = q.shape
     num_pages, nkv, page_size, hd2 = k_cache.shape
-    if hd2 != hd or out.shape != q.shape or out.dtype != q.dtype or k_cache.dtype != q.dtype:
+    vd = v_cache.shape[3]
+    if (hd2 != hd or tuple(out.shape) != (T, nq, vd) or out.dtype != q.dtype or k_cache.dtype != q.dtype
+            or v_cache.dtype != q.dtype or tuple(v_cache.shape[:3]) != (num_pages, nkv, page_size)):
         raise ValueError("paged_attention: shape/dtype mismatch")
     _check(lib().qb_paged_attention_simt(
         _p(q), _code(q), _p(k_cache), _p(v_cache), _p(out), _p(tok_pos), _p(tok_req), _p(block_table),
-        block_table.shape[1], T, nq, nkv, hd, page_size, num_pages, ctypes.c_float(scale), int(window),
+        block_table.shape[1], T, nq, nkv, hd, vd, page_size, num_pages, ctypes.c_float(scale), int(window),
         _p(status), _stream()), "paged_attention_simt")
 
 
@@ -303,8 +389,14 @@ def router_gemm_mma(x: torch.Tensor, pieces: torch.Tensor, logits: torch.Tensor)
     _check(lib().qb_router_gemm_mma(_p(x), _p(pieces), _p(logits), T, E, K, _stream()), "router_gemm_mma")
 
 
-def router_topk(logits, bias, idx_out, w_out, renorm: bool, scale: float) -> None:
-    """``logits`` [T, E], or [P, T, E] partial sums that are added in index order first."""
+ROUTE_SIGMOID_RAW, ROUTE_SIGMOID_RENORM, ROUTE_SOFTMAX_CHOSEN = 0, 1, 2
+
+
+def router_topk(logits, bias, idx_out, w_out, renorm, scale: float) -> None:
+    """``logits`` [T, E], or [P, T, E] partial sums that are added in index order first.  ``renorm``: False / True
+    (sigmoid scores as they are / divided by their sum; the bias enters the choice only), or
+    ``ROUTE_SOFTMAX_CHOSEN``: the choice is by ``logit + bias`` and the weights are the softmax over the chosen
+    values."""
     _want(logits, torch.float32, "logits"); _want(idx_out, torch.int32, "idx_out"); _want(w_out, torch.float32, "w_out")
     n_partials = 1 if logits.dim() == 2 else logits.shape[0]
     T, E = logits.shape[-2:]
@@ -372,7 +464,8 @@ def moe_plan(idx, n_experts: int, bm: int, plan, sorted_pair, tile_expert, tile_
 def moe_grouped_simt(mode: int, x, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
                      n_experts: int, top_k: int) -> None:
     """mode 1: ``out[p, :I] = silu(x[tok] W13_e[:I]^T) * (x[tok] W13_e[I:]^T)``; mode 2:
-    ``out[pair] = w[pair] * (x[p] W2_e^T)``; rows p sorted by expert (see ``moe_plan``)."""
+    ``out[pair] = w[pair] * (x[p] W2_e^T)``; mode 3: ``out[p] = relu(x[tok] W1_e^T)^2`` (ungated experts);
+    rows p sorted by expert (see ``moe_plan``)."""
     K = x.shape[1]
     N = out.shape[1]
     want = (n_experts, 2 * N, K) if mode == 1 else (n_experts, N, K)
@@ -417,8 +510,9 @@ def gather_rows(x, out, sorted_pair, top_k: int) -> None:
 def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, tile_expert, tile_row0,
                    n_experts: int, tile_rows: int, status, gather_top_k: int = 0) -> None:
     """Expert products on tcgen05/TMEM fed by TMA.  ``x_rows`` bf16 [pairs, K] in expert order; mode 1:
-    ``out[p, :I] = silu(gate) * up`` (bf16), mode 2: ``out[pair(p)] = w[pair(p)] * down`` (float32).  The plan's
-    tile list must have been made with ``bm = tile_rows``.  Mode 1 with ``gather_top_k`` > 0: ``x_rows`` is the
+    ``out[p, :I] = silu(gate) * up`` (bf16), mode 2: ``out[pair(p)] = w[pair(p)] * down`` (float32), mode 3:
+    ``out[p] = relu(up)^2`` (bf16; ungated experts, weights ``[E, I, K]``).  The plan's
+    tile list must have been made with ``bm = tile_rows``.  Mode 1 or 3 with ``gather_top_k`` > 0: ``x_rows`` is the
     step's activations [T, K] and the kernel fetches the row of token ``pair // gather_top_k`` itself, one
     TMA box a row (for steps of few tokens: it saves the gathered copy and its launch)."""
     n_x, K = x_rows.shape
@@ -430,7 +524,7 @@ def expert_gemm_tc(mode: int, x_rows, weights, out, sorted_pair, pair_w, plan, t
     if gather_top_k == 0 and n_x != n_pairs:
         raise ValueError(f"expert_gemm_tc: {n_x} rows for {n_pairs} pairs")
     _want(x_rows, torch.bfloat16, "x_rows"); _want(weights, torch.bfloat16, "weights")
-    _want(out, torch.bfloat16 if mode == 1 else torch.float32, "out")
+    _want(out, torch.float32 if mode == 2 else torch.bfloat16, "out")
     _check(lib().qb_expert_gemm_tc(mode, _p(x_rows), _p(weights), _p(out), _p(sorted_pair), _p(pair_w), _p(plan),
                                    _p(tile_expert), _p(tile_row0), tile_expert.numel(), n_pairs, n_experts, K, N,
                                    int(tile_rows), int(gather_top_k), n_x, _p(status), _stream()), "expert_gemm_tc")
@@ -546,15 +640,46 @@ def delta_rule(proj, offsets, wpre, a_bias, w_bias, state, out, req_start, req_s
                                _stream()), "delta_rule", 2)
 
 
-def head_norm_gate(o, proj, gate_off: int, gain, out, n_heads: int, dim: int, eps: float) -> None:
-    """``out[t, h] = o[t, h] / rms(o[t, h]) * gain[h] * sigmoid(proj[t, gate_off + h*dim ...])``."""
+def head_norm_gate(o, proj, gate_off: int, gain, out, n_heads: int, dim: int, eps: float, gate: str = "sigmoid") -> None:
+    """``out[t, h] = o[t, h] / rms(o[t, h]) * gain * act(proj[t, gate_off + h*dim ...])``; ``gain`` has
+    ``n_heads * dim`` elements, or ``dim`` that every head shares; ``gate``: ``"sigmoid"`` or ``"silu"``."""
     _want(o, torch.float32, "o"); _want(proj, torch.float32, "proj"); _want(gain, torch.float32, "gain")
     T = proj.shape[0]
-    if o.numel() != T * n_heads * dim or tuple(out.shape) != (T, n_heads * dim) or gain.numel() != n_heads * dim:
+    if o.numel() != T * n_heads * dim or tuple(out.shape) != (T, n_heads * dim) or gain.numel() not in (n_heads * dim, dim):
         raise ValueError("head_norm_gate: shape mismatch")
-    gate = ctypes.c_void_p(proj.data_ptr() + 4 * int(gate_off))
-    _check(lib().qb_head_norm_gate(_p(o), gate, int(proj.stride(0)), _p(gain), _p(out), _code(out), T, n_heads, dim,
-                                   ctypes.c_float(eps), _stream()), "head_norm_gate")
+    if gate not in ("sigmoid", "silu"):
+        raise ValueError(f"head_norm_gate: gate {gate!r} is not 'sigmoid' or 'silu'")
+    shared = int(gain.numel() == dim and n_heads > 1)
+    gate_ptr = ctypes.c_void_p(proj.data_ptr() + 4 * int(gate_off))
+    _check(lib().qb_head_norm_gate(_p(o), gate_ptr, int(proj.stride(0)), _p(gain), _p(out), _code(out), T, n_heads, dim,
+                                   ctypes.c_float(eps), shared, int(gate == "silu"), _stream()), "head_norm_gate")
+
+
+GLA_MAX_DIM = 256
+
+
+def gla(proj, offsets, inner_off: int, rank: int, w2, bias, state, out, req_start, req_slot, n_heads: int, dim: int,
+        vdim: int, tau: float, q_scale: float) -> None:
+    """Gated linear attention ``S <- diag(alpha) S + k v^T``, ``o = q_scale * S^T q`` per (request, head) over the
+    step's tokens, from and into ``state`` ``[slots, heads, dim, vdim]`` float32.  ``proj`` float32 ``[T, P]`` holds
+    q, k (heads x dim) and v (heads x vdim) at the column ``offsets`` (q, k, v) and the ``rank`` inner values of
+    the decay at ``inner_off``; ``alpha = sigmoid(w2 inner + bias) ^ (1 / tau)`` with ``w2`` ``[heads*dim, rank]``
+    and ``bias`` float32; ``out`` float32 ``[T, heads, vdim]``."""
+    for t, n in ((proj, "proj"), (bias, "bias"), (state, "state"), (out, "out")):
+        _want(t, torch.float32, n)
+    T = proj.shape[0]
+    HD, HE = n_heads * dim, n_heads * vdim
+    q_off, k_off, v_off = (int(o) for o in offsets)
+    if (out.numel() != T * HE or bias.numel() != HD or tuple(w2.shape) != (HD, rank)
+            or tuple(state.shape[1:]) != (n_heads, dim, vdim) or proj.stride(1) != 1
+            or any(o < 0 or o + n > proj.shape[1] for o, n in ((q_off, HD), (k_off, HD), (v_off, HE), (inner_off, rank)))):
+        raise ValueError("gla: shape mismatch")
+    R = req_slot.numel()
+    scratch = torch.empty(T * HD, dtype=torch.float32, device=proj.device)      # alpha of every (token, channel)
+    _check(lib().qb_gla(ctypes.c_void_p(proj.data_ptr()), int(proj.stride(0)), q_off, k_off, v_off, int(inner_off),
+                        int(rank), _p(w2), _code(w2), _p(bias), _p(state), _p(out), _p(scratch), _p(req_start),
+                        _p(req_slot), R, T, n_heads, dim, vdim, ctypes.c_float(tau), ctypes.c_float(q_scale),
+                        _stream()), "gla", 2)
 
 
 def tanh_cols(x, off: int, n: int, out) -> None:

@@ -6,6 +6,12 @@ RMSNorm before the rotation, either over the concatenated heads (``"per_layer"``
 ``rotary_dim`` dims by the position encoding part; K (rotated) and V appended to the cache; scores
 ``q.k * scale`` over the keys at positions <= the query's (and inside the window, if any), softmax in
 float32, ``P V``; output projection.  q head ``h`` reads kv head ``h // (n_q / n_kv)``.
+
+Options beside that formula, all off by default: values of another head size than the keys
+(``value_dim``); a query temperature ``q *= 1 + coef * ln(floor((p + 1) / every) + 1)`` at position p
+(``q_temperature``); a gate per head, ``out_h *= sigmoid(W_g x)_h`` before the output projection (tensor
+``names["g"]``, ``[heads, hidden]``, part of the fused input projection); a layer without keys and values
+of its own (``own_kv`` False: no k/v tensors; the model's run order names the entry whose cache it reads).
 """
 
 from __future__ import annotations
@@ -14,7 +20,7 @@ import torch
 
 from .. import kernels
 from ..matmul import empty_rows, linear
-from .base import KVCacheSpec, Mixer, TensorSpec, make, register
+from .base import CacheSpec, CacheStream, KeepAll, Mixer, TensorSpec, Window, make, register
 
 _NORM_KIND = {None: kernels.NORM_NONE, "per_layer": kernels.NORM_PER_LAYER, "per_head": kernels.NORM_PER_HEAD}
 
@@ -24,18 +30,28 @@ class GQAttention(Mixer):
     graph_safe = True
 
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                 position, qk_norm: str | None, qk_norm_eps: float, names: dict, window: int | None = None):
+                 position, qk_norm: str | None, qk_norm_eps: float, names: dict, window: int | None = None,
+                 value_dim: int | None = None, q_temperature: tuple | None = None, own_kv: bool = True,
+                 float32_output: bool = False):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} q heads are not a multiple of {n_kv_heads} kv heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        value_dim = head_dim if value_dim is None else int(value_dim)
+        if not 0 < head_dim <= 256 or not 0 < value_dim <= 256:
+            raise ValueError(f"head sizes {head_dim} / {value_dim}: the attention kernels take 1 to 256")
         if qk_norm not in _NORM_KIND:
             raise ValueError(f"qk_norm {qk_norm!r} is not None, 'per_layer' or 'per_head'")
         self.hidden, self.nq, self.nkv, self.hd = int(hidden_size), int(n_q_heads), int(n_kv_heads), int(head_dim)
+        self.vd, self.own_kv, self.float32_output = value_dim, bool(own_kv), bool(float32_output)
         self.scale, self.qk_norm, self.eps = float(scale), qk_norm, float(qk_norm_eps)
         self.window = window
+        self.q_temp = (0.0, 0) if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+        if self.q_temp[1] < 0:
+            raise ValueError(f"q_temperature every {self.q_temp[1]} must be positive (0: none)")
         self.position = make("position", position) if isinstance(position, tuple) else position
-        self.names = dict(names)      # q, k, v, o, and q_norm, k_norm when normed
+        self.names = dict(names)      # q, o; k, v with own_kv; q_norm (k_norm) when normed; g for a gate per head
+        self.gated = "g" in self.names
+        # the tensor-core kernels take equal key and value head sizes that are multiples of 16
+        self.mma_shapes = self.hd == self.vd and self.hd % 16 == 0
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
         # more q heads per kv head than the single-token kernel takes: single tokens run as portions of one,
         # whose tile list comes from the host each step, so such a model's decode steps are not captured
@@ -45,31 +61,46 @@ class GQAttention(Mixer):
         return [self.position]
 
     def tensor_specs(self):
-        n, H, hd = self.names, self.hidden, self.hd
-        specs = [TensorSpec(n["q"], (self.nq * hd, H)), TensorSpec(n["k"], (self.nkv * hd, H)),
-                 TensorSpec(n["v"], (self.nkv * hd, H)), TensorSpec(n["o"], (H, self.nq * hd))]
-        if self.qk_norm == "per_layer":
-            specs += [TensorSpec(n["q_norm"], (self.nq * hd,), "f32", "gain"),
-                      TensorSpec(n["k_norm"], (self.nkv * hd,), "f32", "gain")]
-        elif self.qk_norm == "per_head":
-            specs += [TensorSpec(n["q_norm"], (hd,), "f32", "gain"), TensorSpec(n["k_norm"], (hd,), "f32", "gain")]
+        n, H, hd, vd = self.names, self.hidden, self.hd, self.vd
+        specs = [TensorSpec(n["q"], (self.nq * hd, H)), TensorSpec(n["o"], (H, self.nq * vd))]
+        if self.own_kv:
+            specs += [TensorSpec(n["k"], (self.nkv * hd, H)), TensorSpec(n["v"], (self.nkv * vd, H))]
+        if self.gated:
+            specs.append(TensorSpec(n["g"], (self.nq, H)))
+        if self.qk_norm is not None:
+            specs.append(TensorSpec(n["q_norm"], (self.nq * hd if self.qk_norm == "per_layer" else hd,), "f32", "gain"))
+            if self.own_kv:
+                specs.append(TensorSpec(n["k_norm"], (self.nkv * hd if self.qk_norm == "per_layer" else hd,), "f32", "gain"))
         return specs
 
     def load(self, fetch):
         n = self.names
         q = fetch(n["q"])
-        self.w_qkv = torch.empty(((self.nq + 2 * self.nkv) * self.hd, self.hidden), dtype=q.dtype, device=q.device)
-        a, b = self.nq * self.hd, (self.nq + self.nkv) * self.hd
+        # the rows of the fused input projection: q, then k and v where the layer has its own, then the gates;
+        # padded to a multiple of 8 so that every row of the product starts on 16 bytes
+        a = self.nq * self.hd
+        b = a + (self.nkv * self.hd if self.own_kv else 0)
+        c = b + (self.nkv * self.vd if self.own_kv else 0)
+        self.gate_off = c
+        rows = c + (self.nq if self.gated else 0)
+        self.w_qkv = torch.zeros((-(-rows // 8) * 8, self.hidden), dtype=q.dtype, device=q.device)
         self.w_qkv[:a].copy_(q)
         del q
-        self.w_qkv[a:b].copy_(fetch(n["k"]))
-        self.w_qkv[b:].copy_(fetch(n["v"]))
+        if self.own_kv:
+            self.w_qkv[a:b].copy_(fetch(n["k"]))
+            self.w_qkv[b:c].copy_(fetch(n["v"]))
+        if self.gated:
+            self.w_qkv[c:rows].copy_(fetch(n["g"]))
         self.w_o = fetch(n["o"])
         if self.qk_norm is not None:
-            self.q_norm_w, self.k_norm_w = fetch(n["q_norm"]), fetch(n["k_norm"])
+            self.q_norm_w = fetch(n["q_norm"])
+            self.k_norm_w = fetch(n["k_norm"]) if self.own_kv else None
 
     def cache_spec(self):
-        return KVCacheSpec(self.nkv, self.hd, self.window)
+        if not self.own_kv:
+            return None
+        return CacheSpec((CacheStream("k", self.nkv, self.hd), CacheStream("v", self.nkv, self.vd)),
+                         KeepAll() if self.window is None else Window(int(self.window)))
 
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
@@ -84,20 +115,31 @@ class GQAttention(Mixer):
             if ctx.positions.dim() != 2 or ctx.positions.shape[1] < n_axes:
                 raise ValueError(f"the position encoding reads {n_axes} position axes; the step gives "
                                  f"{tuple(ctx.positions.shape)}")
+        if cache is None or (cache.write and not self.own_kv):
+            raise ValueError("an attention layer without keys and values of its own must be given another "
+                             "entry's cache to read (ScheduleEntry.read_cache_of)")
+        if tuple(cache.k.shape[1:]) != (self.nkv, cache.page_size, self.hd) or cache.v.shape[3] != self.vd:
+            raise ValueError(f"the cache holds keys {tuple(cache.k.shape[1:])} and values of {cache.v.shape[3]}; this "
+                             f"layer reads {self.nkv} heads of {self.hd} / {self.vd}")
         kernels.qknorm_rope_write(
             qkv, q, cache.k if cache.write else None, cache.v if cache.write else None, self.q_norm_w,
             self.k_norm_w, _NORM_KIND[self.qk_norm], self.eps, inv_freq, pair_axis, ctx.positions, ctx.tok_pos,
-            ctx.tok_req, cache.block_table, self.nq, self.nkv, self.hd, rd, cache.page_size, ctx.status)
-        out = empty_rows(T, self.nq, self.hd, dtype=x.dtype, device=x.device)
+            ctx.tok_req, cache.block_table, self.nq, self.nkv, self.hd, rd, cache.page_size, ctx.status,
+            vd=self.vd, has_kv=self.own_kv, q_temp_coef=self.q_temp[0], q_temp_every=self.q_temp[1])
+        out = empty_rows(T, self.nq, self.vd, dtype=x.dtype, device=x.device)
         self.attend(q, cache, out, ctx)
-        return linear(out.view(T, self.nq * self.hd), self.w_o)
+        if self.gated:
+            kernels.head_sigmoid_gate(out, qkv[:, self.gate_off: self.gate_off + self.nq], self.nq, self.vd)
+        return linear(out.view(T, self.nq * self.vd), self.w_o,
+                      out_dtype=torch.float32 if self.float32_output else None)
 
     def attend(self, q, cache, out, ctx):
-        """float32: the SIMT kernel, every token alike.  bfloat16: tensor-core kernels, one for single
+        """float32 (and head sizes the tensor-core kernels do not take: keys and values of different sizes, or
+        no multiple of 16): the SIMT kernel, every token alike.  bfloat16: tensor-core kernels, one for single
         tokens (the keys of all of them dealt evenly over the SMs) and one for portions (tiles of
         token-by-head rows)."""
         window = self.window or 0
-        if q.dtype != torch.bfloat16:
+        if q.dtype != torch.bfloat16 or not self.mma_shapes:
             kernels.paged_attention_simt(q, cache.k, cache.v, out, ctx.tok_pos, ctx.tok_req, cache.block_table,
                                          self.scale, window, ctx.status)
             return

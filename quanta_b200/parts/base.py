@@ -57,7 +57,8 @@ class TensorSpec:
     ``kind``: ``"matrix"`` is held in the model's compute dtype (bfloat16 or float32); ``"f32"`` is
     held in float32 whatever the compute dtype (norm gains, router gate and bias: a tensor stored in
     32-bit stays so); ``"i32"`` integer tables.  ``init`` tells the random-weights mode how to draw
-    it: ``"normal"`` N(0, 0.02), ``"gain"`` 1 + U(-0.1, 0.1), ``"bias"`` U(-0.05, 0.05).
+    it: ``"normal"`` N(0, 0.02), ``"gain"`` 1 + U(-0.1, 0.1), ``"bias"`` U(-0.05, 0.05), ``"mixing"`` a square matrix, the
+    identity + U(-0.1, 0.1).
     """
     name: str
     shape: tuple[int, ...]
@@ -204,10 +205,27 @@ class NormedPending:
         return d
 
 
+class StreamsPending:
+    """A pending contribution of a model that keeps several residual streams ``x_1 .. x_S``: the sublayer's output
+    ``y`` (``[T, H]``, or ``[T, K, H]`` partial results that are added in order) and how it is written back,
+    ``x_t <- sum_s mix[s, t] x_s + mult * out_w[t] * y`` for all streams at once.  The norm that reads the streams
+    next does the write-back in its own launch (``Norm.forward_streams``; a plain ``forward`` of the built-in
+    norm reads the sum of the streams, which is what the output head wants)."""
+
+    def __init__(self, y: torch.Tensor, mix: torch.Tensor, out_w: torch.Tensor, mult: float):
+        self.y, self.mix, self.out_w, self.mult = y, mix, out_w, float(mult)
+
+
 class Norm(Part):
     def forward(self, h: torch.Tensor, delta, out, rows=None, store_h=True) -> None:
-        """``delta``: None, a tensor ``[T, H]`` / ``[T, S, H]``, or a ``NormedPending``."""
+        """``delta``: None, a tensor ``[T, H]`` / ``[T, S, H]``, a ``NormedPending``, or (with ``h`` the streams
+        ``[T, S, H]`` of a model that keeps several) a ``StreamsPending``."""
         raise NotImplementedError
+
+    def forward_streams(self, x: torch.Tensor, pending, read_w, out, rows=None, store=True) -> None:
+        """Several residual streams ``x`` ``[T, S, H]``: write ``pending`` (a ``StreamsPending`` or None) back,
+        read ``u = sum_t read_w[t] x_t`` (``read_w`` None: the plain sum) and norm ``u`` into ``out``."""
+        raise NotImplementedError(f"{type(self).__name__} does not read several residual streams")
 
 
 class PositionEncoding(Part):

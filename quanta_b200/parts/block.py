@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels
 from ..matmul import empty_rows, linear
-from .base import Block, Embedding, Head, NormedPending, TensorSpec, make, register
+from .base import Block, Embedding, Head, NormedPending, StreamsPending, TensorSpec, make, register
 
 
 @register("block", "pre_norm")
@@ -93,26 +93,111 @@ class SandwichNormBlock(Block):
         return NormedPending(self.feed_forward.forward(x2, ctx), self.feed_forward_post_norm)
 
 
-@register("embedding", "token_table")
-class TokenTable(Embedding):
-    """``h = table[ids] * scale`` into the float32 residual stream (src/quanta/minimax/model.py:91; the
-    reference has no scale)."""
+@register("block", "hyper_connected")
+class HyperConnectedBlock(Block):
+    """Pre-norm sublayers over ``streams`` copies ``x_1 .. x_S`` of the residual stream.  Sublayer q (the mixer,
+    then the feed-forward where the layer has one) reads ``u = sum_s in_q[s] x_s``, computes
+    ``y = sublayer(norm_q(u))`` and writes back ``x_t <- sum_s mix_q[s, t] x_s + mult * out_q[t] * y`` for all
+    streams at once (``mix_q`` is indexed ``[from, to]``).  ``names`` gives the tensors ``in1, mix1, out1, in2,
+    mix2, out2``; None: unit weights and the identity, which with one stream is the usual pre-norm residual
+    ``x += mult * sublayer(norm(x))``.  Streams, sums and norms are float32; the write-back of a sublayer, the
+    read of the next and its norm are one launch (the model's head reads the sum of the streams the same way)."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, scale: float = 1.0):
-        self.V, self.H, self.weight_name, self.scale = int(vocab_size), int(hidden_size), weight_name, float(scale)
-        self.table = None
+    def __init__(self, hidden_size: int, streams: int, mixer, mixer_norm, feed_forward=None, feed_forward_norm=None,
+                 residual_mult: float = 1.0, names: dict | None = None):
+        if not 1 <= int(streams) <= kernels.MAX_STREAMS:
+            raise ValueError(f"{streams} residual streams: the kernel takes 1 to {kernels.MAX_STREAMS}")
+        self.hidden, self.S, self.mult = int(hidden_size), int(streams), float(residual_mult)
+        self.mixer = make("mixer", mixer)
+        self.mixer_norm = make("norm", mixer_norm)
+        self.feed_forward = make("feed_forward", feed_forward) if feed_forward is not None else None
+        self.feed_forward_norm = make("norm", feed_forward_norm) if feed_forward is not None else None
+        self.names = dict(names) if names is not None else None
+        self.w: dict[str, torch.Tensor] = {}
+
+    def _sublayers(self):
+        return ("1", "2") if self.feed_forward is not None else ("1",)
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
 
     def tensor_specs(self):
-        return [TensorSpec(self.weight_name, (self.V, self.H))]
+        if self.names is None:
+            return []
+        specs = []
+        for q in self._sublayers():
+            specs += [TensorSpec(self.names["in" + q], (self.S,), "f32", "gain"),
+                      TensorSpec(self.names["mix" + q], (self.S, self.S), "f32", "mixing"),
+                      TensorSpec(self.names["out" + q], (self.S,), "f32", "gain")]
+        return specs
+
+    def load(self, fetch):
+        if self.names is not None:
+            for q in self._sublayers():
+                for k in ("in", "mix", "out"):
+                    self.w[k + q] = fetch(self.names[k + q]).contiguous()
+
+    def _weights(self, device):
+        if not self.w:
+            for q in self._sublayers():
+                self.w["in" + q] = torch.ones(self.S, dtype=torch.float32, device=device)
+                self.w["mix" + q] = torch.eye(self.S, dtype=torch.float32, device=device)
+                self.w["out" + q] = torch.ones(self.S, dtype=torch.float32, device=device)
+        return self.w
+
+    def forward(self, h, pending, ctx, cache, state):
+        x = h if h.dim() == 3 else h.unsqueeze(1)
+        if x.shape[1] != self.S:
+            raise ValueError(f"the layer is connected to {self.S} residual streams; the model keeps {x.shape[1]}")
+        w = self._weights(h.device)
+        T = x.shape[0]
+        u = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
+        self.mixer_norm.forward_streams(x, pending, w["in1"], u)
+        d = StreamsPending(self.mixer.forward(u, ctx, cache, state), w["mix1"], w["out1"], self.mult)
+        if self.feed_forward is None:
+            return d
+        u2 = empty_rows(T, self.hidden, dtype=ctx.dtype, device=h.device)
+        self.feed_forward_norm.forward_streams(x, d, w["in2"], u2)
+        return StreamsPending(self.feed_forward.forward(u2, ctx), w["mix2"], w["out2"], self.mult)
+
+
+@register("embedding", "token_table")
+class TokenTable(Embedding):
+    """``h = table[ids] * scale`` into the float32 residual stream (src/quanta/minimax/model.py:91; the
+    reference has no scale).  ``positions_name``: a second table ``[max_positions, hidden]`` whose row of the
+    token's position is added (not scaled).  ``streams`` > 1: the model keeps that many residual streams, which
+    all start as this row (``[T, streams, hidden]``)."""
+
+    graph_safe = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, scale: float = 1.0,
+                 positions_name: str | None = None, max_positions: int = 0, streams: int = 1):
+        self.V, self.H, self.weight_name, self.scale = int(vocab_size), int(hidden_size), weight_name, float(scale)
+        self.positions_name, self.max_positions, self.streams = positions_name, int(max_positions), int(streams)
+        if positions_name is not None and self.max_positions <= 0:
+            raise ValueError("a table of learned positions needs max_positions")
+        self.table = self.pos_table = None
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.weight_name, (self.V, self.H))]
+        if self.positions_name is not None:
+            specs.append(TensorSpec(self.positions_name, (self.max_positions, self.H)))
+        return specs
 
     def load(self, fetch):
         self.table = fetch(self.weight_name)
+        if self.positions_name is not None:
+            self.pos_table = fetch(self.positions_name)
 
     def forward(self, ids, ctx):
-        h = torch.empty((ids.numel(), self.H), dtype=torch.float32, device=ids.device)
-        kernels.embedding(h, self.table, ids, ctx.status, self.scale)
+        shape = (ids.numel(), self.H) if self.streams == 1 else (ids.numel(), self.streams, self.H)
+        if self.pos_table is not None and ctx.host and ctx.max_len_after > self.max_positions:
+            raise ValueError(f"a request of {ctx.max_len_after} tokens: the model has learned positions for "
+                             f"{self.max_positions}")
+        h = torch.empty(shape, dtype=torch.float32, device=ids.device)
+        kernels.embedding(h, self.table, ids, ctx.status, self.scale, self.pos_table, ctx.tok_pos)
         return h
 
 
@@ -120,12 +205,13 @@ class TokenTable(Embedding):
 class LinearHead(Head):
     """Final norm on the wanted rows, then ``logits = x @ head.T`` in float32
     (src/quanta/minimax/runtime.py:95-98).  ``tied_to`` names the embedding table to reuse (a tensor that
-    two parts ask for by the same name is loaded once and shared)."""
+    two parts ask for by the same name is loaded once and shared); ``logit_scale`` multiplies the logits."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, norm, weight_name: str | None, tied_to: str | None):
-        self.V, self.H = int(vocab_size), int(hidden_size)
+    def __init__(self, vocab_size: int, hidden_size: int, norm, weight_name: str | None, tied_to: str | None,
+                 logit_scale: float = 1.0):
+        self.V, self.H, self.logit_scale = int(vocab_size), int(hidden_size), float(logit_scale)
         self.norm = make("norm", norm)
         self.weight_name, self.tied_to = weight_name, tied_to
         self.weight = None
@@ -143,4 +229,7 @@ class LinearHead(Head):
         n = rows.numel()
         x = empty_rows(n, self.H, dtype=ctx.dtype, device=h.device)
         self.norm.forward(h, pending, x, rows=rows, store_h=False)
-        return linear(x, self.weight, out_dtype=torch.float32)
+        logits = linear(x, self.weight, out_dtype=torch.float32)
+        if self.logit_scale != 1.0:
+            logits.mul_(self.logit_scale)       # on the float32 products: one rounding, as the formula has it
+        return logits

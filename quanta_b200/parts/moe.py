@@ -1,10 +1,14 @@
-"""Feed-forward part: sigmoid-routed SwiGLU experts.
+"""Feed-forward parts: routed experts (sigmoid-routed SwiGLU experts; softmax-routed ungated experts).
 
 Routed experts (src/quanta/minimax/moe.py:36-88): router logits in float32 from a float32 gate;
 ``sigmoid`` scores; a correction bias added for the choice only; top-k (ties to the lower expert
 index); weights are the bias-free scores, renormalised (``+ 1e-20``) and scaled; each chosen expert is
 ``down(silu(gate x) * up x)`` (``w1`` gate, ``w3`` up, ``w2`` down); the weight is applied after
 ``down``; the k results are summed in float32 in slot order.  No shared expert.
+
+``softmax_topk_experts`` shares the plan and the kernels: the router has a bias that is part of the logits
+(``z = gate x + bias``, float32), the ``top_k`` largest logits choose, the weights are the softmax over the
+chosen logits only, and an expert is ungated, ``down(relu(up x)^2)``.
 """
 
 from __future__ import annotations
@@ -22,6 +26,9 @@ class SigmoidTopKExperts(FeedForward):
     """``trace``: a list assigned here receives, for every step, the experts each token chose (int32
     ``[T, k]`` on the device, in choice order), for tools that follow the routing; while it is set the
     part is not graph-safe, so an engine built then runs its decode steps kernel by kernel."""
+
+    # the first product of an expert: 1 = silu(gate x) * (up x) from [gate; up] rows, 3 = relu(up x)^2
+    first_product_mode = 1
 
     @property
     def graph_safe(self):
@@ -157,17 +164,55 @@ class SigmoidTopKExperts(FeedForward):
             # bfloat16: TMA-fed tcgen05 products, weights as the 128-row operand, accumulators in TMEM
             if n_pairs <= self.gather_in_kernel_max_rows * self.E:
                 # few tokens: the kernel fetches each pair's token row itself
-                kernels.expert_gemm_tc(1, x, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert,
-                                       tile_row0, self.E, bm, ctx.status, gather_top_k=self.k)
+                kernels.expert_gemm_tc(self.first_product_mode, x, self.w13, act, sorted_pair, w.view(-1), plan,
+                                       tile_expert, tile_row0, self.E, bm, ctx.status, gather_top_k=self.k)
             else:
                 xg = torch.empty((n_pairs, self.H), dtype=x.dtype, device=dev)
                 kernels.gather_rows(x, xg, sorted_pair, self.k)
-                kernels.expert_gemm_tc(1, xg, self.w13, act, sorted_pair, w.view(-1), plan, tile_expert, tile_row0,
-                                       self.E, bm, ctx.status)
+                kernels.expert_gemm_tc(self.first_product_mode, xg, self.w13, act, sorted_pair, w.view(-1), plan,
+                                       tile_expert, tile_row0, self.E, bm, ctx.status)
             kernels.expert_gemm_tc(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
                                    tile_expert, tile_row0, self.E, bm, ctx.status)
         else:
-            kernels.moe_grouped_simt(1, x, self.w13, act, sorted_pair, w, plan, tile_expert, tile_row0, self.E, self.k)
+            kernels.moe_grouped_simt(self.first_product_mode, x, self.w13, act, sorted_pair, w, plan, tile_expert,
+                                     tile_row0, self.E, self.k)
             kernels.moe_grouped_simt(2, act, self.w2, y.view(n_pairs, self.H), sorted_pair, w.view(-1), plan,
                                      tile_expert, tile_row0, self.E, self.k)
         return y
+
+
+@register("feed_forward", "softmax_topk_experts")
+class SoftmaxTopKExperts(SigmoidTopKExperts):
+    """Router logits ``z = gate x + bias`` (float32); the ``top_k`` largest choose (the lower index among equals);
+    the weights are the softmax over the chosen logits only; an expert is ``down(relu(up x)^2)`` without biases.
+    ``names``: gate, bias (when ``use_bias``), and the templates up / down with ``{e}``."""
+
+    first_product_mode = 3
+
+    def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top_k: int, use_bias: bool, names: dict):
+        super().__init__(hidden_size, expert_size, n_experts, top_k, use_bias, renormalize=True, scaling=1.0, names=names)
+        self.renorm = kernels.ROUTE_SOFTMAX_CHOSEN       # how the routing kernels weight the chosen experts
+
+    def tensor_specs(self):
+        n = self.names
+        specs = [TensorSpec(n["gate"], (self.E, self.H), "f32", "normal")]
+        if self.use_bias:
+            specs.append(TensorSpec(n["bias"], (self.E,), "f32", "bias"))
+        for e in range(self.E):
+            specs += [TensorSpec(n["up"].format(e=e), (self.I, self.H)), TensorSpec(n["down"].format(e=e), (self.H, self.I))]
+        return specs
+
+    def load(self, fetch):
+        n = self.names
+        self.gate_w = fetch(n["gate"])
+        self.bias = fetch(n["bias"]) if self.use_bias else None
+        first = fetch(n["up"].format(e=0))
+        dt, dev = first.dtype, first.device
+        self.w13 = torch.empty((self.E, self.I, self.H), dtype=dt, device=dev)      # the up rows alone
+        self.w2 = torch.empty((self.E, self.H, self.I), dtype=dt, device=dev)
+        for e in range(self.E):
+            self.w13[e].copy_(first if e == 0 else fetch(n["up"].format(e=e)))
+            self.w2[e].copy_(fetch(n["down"].format(e=e)))
+        del first
+        if dt == torch.bfloat16 and self.H % 8 == 0 and self.gate_w.is_cuda:
+            self.gate_pieces = kernels.split3_bf16(self.gate_w)

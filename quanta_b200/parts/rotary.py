@@ -44,3 +44,13 @@ class PartialRotary(PositionEncoding):
                 axis = axis.to(device)
             self._tables[key] = (inv, axis, self.rotary_dim, self.n_axes)
         return self._tables[key]
+
+
+@register("position", "none")
+class NoPosition(PositionEncoding):
+    """Nothing is rotated: positions reach the mixer some other way (a learned table, a query temperature)."""
+
+    graph_safe = True
+
+    def rotary_tables(self, device):
+        return None
