@@ -48,14 +48,18 @@ def dense_ff(h, up, down):
     return relu_squared(h @ up.T) @ down.T
 
 
-def routed_ff(h, router, router_bias, ups, downs, top: int):
+def routed_ff(h, router, router_bias, ups, downs, top: int, chosen=None):
     """Logits ``router h + bias``; the ``top`` largest are chosen (the lower index on a tie); their weights are
     the softmax over the chosen logits only.  Returns (output, chosen experts [T, top], margin between the
-    last chosen and the first refused logit [T])."""
+    last chosen and the first refused logit [T]).  ``chosen`` [T, top]: take these experts instead of choosing
+    (to follow an implementation whose rounding turned a close choice); the weights are still computed here."""
     z = h @ router.T + router_bias
     order = torch.sort(z, dim=-1, descending=True, stable=True)
     idx, val = order.indices[:, :top], order.values[:, :top]
     margin = (order.values[:, top - 1] - order.values[:, top]) if z.shape[1] > top else torch.full_like(z[:, 0], 1e9)
+    if chosen is not None:
+        idx = torch.as_tensor(chosen, dtype=torch.long, device=z.device)
+        val = torch.gather(z, 1, idx)
     w = torch.softmax(val, -1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -141,9 +145,10 @@ def layer_tensors(weights: dict, prefix: str) -> dict:
     return {k[n:]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, want_layers: bool = False, want_routing: bool = False):
+def forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, want_layers: bool = False, want_routing: bool = False,
+            chosen=None):
     """Logits [T, vocab] (and the sum of the streams after every layer, [layers, T, width]; and per routed
-    layer the (experts, margins))."""
+    layer the (experts, margins)).  ``chosen``: per routed layer, in order, the experts [T, top] to take."""
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(cfg["norm"]["eps"])
     m = float(cfg.get("residual_mult", 1.0))
@@ -175,8 +180,9 @@ def forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, want_layers: 
                 else:
                     keys, values = attention_keys_values(h, mix, mx["kv_heads"], mx["dim"], mx["vdim"], eps)
                     kept[i] = (keys, values)
+                temp = mx.get("q_temp") or {"coef": 0.0, "every": 1}
                 y = attention_mixer(h, mix, keys, values, mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"],
-                                    float(mx["scale"]), float(mx["q_temp"]["coef"]), int(mx["q_temp"]["every"]), eps)
+                                    float(mx["scale"]), float(temp["coef"]), int(temp["every"]), eps)
             else:
                 mlp = layer["mlp"]
                 if mlp["kind"] == "dense":
@@ -185,7 +191,8 @@ def forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, want_layers: 
                     E = int(mlp["router"]["experts"])
                     y, idx, margin = routed_ff(h, W[p + "mlp.router"], W[p + "mlp.router.b"],
                                                [W[f"{p}mlp.e{e}.up"] for e in range(E)],
-                                               [W[f"{p}mlp.e{e}.down"] for e in range(E)], int(mlp["router"]["top"]))
+                                               [W[f"{p}mlp.e{e}.down"] for e in range(E)], int(mlp["router"]["top"]),
+                                               chosen=None if chosen is None else chosen[len(routing)])
                     routing.append((idx, margin))
             streams = connect(streams, y, w_in, w_mix, w_out, m)
         after.append(streams.sum(0))
@@ -197,3 +204,66 @@ def forward(weights: dict, cfg: dict, tokens, dtype=torch.float32, want_layers: 
     if want_routing:
         out.append(routing)
     return out[0] if len(out) == 1 else tuple(out)
+
+
+def greedy(weights: dict, cfg: dict, prompt, n_new: int) -> list[int]:
+    toks, new = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(weights, cfg, toks)[-1].argmax())
+        toks.append(nxt)
+        new.append(nxt)
+    return new
+
+
+def draw_weights(cfg: dict, seed: int, decay_rank: int = 8, matrix_dtype=torch.bfloat16) -> dict:
+    """Random weights for a configuration, at scales where every mechanism matters: projections of unit gain,
+    norm gains around 1, decays spread over (0.5, 1), connection weights away from 1 and the identity, router
+    biases as large as the logits' spread, learned positions as large as the embedded tokens."""
+    g = torch.Generator().manual_seed(seed)
+    W = {}
+    width, vocab = cfg["width"], cfg["vocab"]
+
+    def mat(name, out, inn, gain=1.0):
+        W[name] = (torch.randn(out, inn, generator=g) * gain / math.sqrt(inn)).to(matrix_dtype)
+
+    def vec(name, n, mean=1.0, spread=0.3):
+        W[name] = (mean + spread * torch.randn(n, generator=g)).to(matrix_dtype)
+
+    W["embed"] = (torch.randn(vocab, width, generator=g) * 0.5).to(matrix_dtype)
+    W["pos"] = (torch.randn(cfg["max_positions"], width, generator=g) * 0.5).to(matrix_dtype)
+    vec("final.norm", width)
+    S = int(cfg.get("streams", 0))
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        vec(p + "norm1", width)
+        if layer["type"] == "gla":
+            HD, HE = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            mat(p + "mix.q", HD, width, 2.0); mat(p + "mix.k", HD, width, 2.0); mat(p + "mix.v", HE, width)
+            mat(p + "mix.g", HE, width); mat(p + "mix.o", width, HE)
+            vec(p + "mix.norm", m["vdim"])
+            rank = m.get("decay_rank", decay_rank)
+            mat(p + "mix.a1", rank, width); mat(p + "mix.a2", HD, rank, 2.0)
+            vec(p + "mix.a2.b", HD, mean=2.0, spread=1.5)
+        else:
+            Q = m["heads"] * m["dim"]
+            mat(p + "mix.q", Q, width); vec(p + "mix.q.norm", Q)
+            mat(p + "mix.g", m["heads"], width, 2.0); mat(p + "mix.o", width, m["heads"] * m["vdim"])
+            if m.get("kv_from") is None:
+                K = m["kv_heads"] * m["dim"]
+                mat(p + "mix.k", K, width); mat(p + "mix.v", m["kv_heads"] * m["vdim"], width); vec(p + "mix.k.norm", K)
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            vec(p + "norm2", width)
+            if mlp["kind"] == "dense":
+                mat(p + "mlp.up", mlp["ff"], width); mat(p + "mlp.down", width, mlp["ff"])
+            else:
+                E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+                mat(p + "mlp.router", E, width); vec(p + "mlp.router.b", E, mean=0.0, spread=0.5)
+                for e in range(E):
+                    mat(f"{p}mlp.e{e}.up", ff, width); mat(f"{p}mlp.e{e}.down", width, ff)
+        if S:
+            for q in ("1", "2") if mlp is not None else ("1",):
+                vec(f"{p}hc{q}.in", S, mean=0.6, spread=0.3)
+                vec(f"{p}hc{q}.out", S, mean=0.8, spread=0.4)
+                W[f"{p}hc{q}.mix"] = (0.7 * torch.eye(S) + 0.3 * torch.randn(S, S, generator=g) / math.sqrt(S)).to(matrix_dtype)
+    return W
