@@ -1,4 +1,4 @@
-"""``bench.py --design guravik``: the Guravik decoder beside the MiniMax-M3 decoder at equal sizes.
+"""``bench.py --design guravik`` / ``--design tirizen``: another decoder beside the MiniMax-M3 decoder at equal sizes.
 
 For a few sizes that resemble a real model's layers (seeded random weights, bfloat16): one prompt of
 ``--prompt-len`` tokens as one step (tokens a second) and decode steps of ``--batch`` requests at that
@@ -13,6 +13,13 @@ bandwidth), and the recurrence (state bytes / time / copy bandwidth for single t
 float32 flops a second for a prompt, where it is a chain in time and has no tensor-core form here).
 Times are medians of CUDA-event intervals after warm-up; decode kernels run back to back in a CUDA graph on
 caches of several layers, larger than L2.
+
+``--design tirizen``: the same two model measurements for the Tirizen decoder (layers: attention with routed
+experts, gated linear attention with routed experts, attention that reads the first layer's keys and values;
+three residual streams), whose attention and expert products run on the SAME kernels as MiniMax-M3's at these
+sizes; alone are measured the kernels that are its own: the gated linear recurrence beside Guravik's delta-rule
+recurrence (the like kernel), and the launch between two sublayers (streams written back, read and normed)
+beside the adding RMS norm, both as bytes / time / copy bandwidth.
 """
 
 from __future__ import annotations
@@ -42,6 +49,29 @@ def guravik_raw(s: dict) -> dict:
     return {"architecture": "Guravik", "vocab": s["vocab"], "width": s["width"], "layers": [latent, delta, delta] * s["groups"],
             "canon": {"taps": 3}, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
             "loop": {"start": 0, "stop": 0, "times": 1}}
+
+
+TIRIZEN_SIZES = {
+    "w2048": dict(width=2048, groups=2, vocab=32000, ff=5632, attn_heads=16, dim=128, gla_heads=32, gla_dim=64, streams=3),
+    "w4096": dict(width=4096, groups=2, vocab=32000, ff=11008, attn_heads=32, dim=128, gla_heads=64, gla_dim=64, streams=3),
+}
+
+
+def tirizen_raw(s: dict) -> dict:
+    """Per group of three layers: attention, gated linear attention, attention on the first one's keys and values;
+    every layer with 8 routed experts of which 2 are active, together as wide as ``ff``."""
+    moe = {"kind": "moe", "expert": {"ff": s["ff"] // 2}, "router": {"experts": 8, "top": 2}}
+    layers = []
+    for g in range(s["groups"]):
+        attn = {"heads": s["attn_heads"], "kv_heads": max(1, s["attn_heads"] // 4), "dim": s["dim"], "vdim": s["dim"],
+                "scale": 1.0 / math.sqrt(s["dim"]), "q_temp": {"coef": 0.3, "every": 256}}
+        layers += [{"type": "attention", "mixer": dict(attn), "mlp": moe},
+                   {"type": "gla", "mixer": {"heads": s["gla_heads"], "dim": s["gla_dim"], "vdim": s["gla_dim"], "tau": 16.0,
+                                             "decay_rank": 16}, "mlp": moe},
+                   {"type": "attention", "mixer": dict(attn, kv_from=3 * g), "mlp": moe}]
+    return {"architecture": "Tirizen", "vocab": s["vocab"], "width": s["width"], "layers": layers, "streams": s["streams"],
+            "residual_mult": 0.7, "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "max_positions": 8192}
 
 
 def minimax_raw(s: dict) -> dict:
@@ -179,7 +209,99 @@ def delta_rule(tokens_per_req: int, reqs: int, heads: int, D: int) -> dict:
             "fp32 TFLOP/s": round(8.0 * D * D * heads * T / ms / 1e9, 2)}
 
 
+def gla(tokens_per_req: int, reqs: int, heads: int, D: int, E: int, rank: int = 16) -> dict:
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    T, HD, HE = tokens_per_req * reqs, heads * D, heads * E
+    proj = torch.randn(T, 2 * HD + 2 * HE + rank, device=dev)
+    w2 = torch.randn(HD, rank, device=dev, dtype=torch.bfloat16)
+    bias = torch.full((HD,), 3.0, device=dev)
+    layers = 1 if tokens_per_req > 1 else max(1, min(16, int(2e9 // (reqs * heads * D * E * 4))))
+    states = [torch.zeros(reqs, heads, D, E, device=dev) for _ in range(layers)]
+    out = torch.empty(T, heads, E, device=dev)
+    starts = torch.arange(0, T + 1, tokens_per_req, dtype=torch.int32, device=dev)
+    slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+
+    def all_layers():
+        for s in states:
+            k.gla(proj, (0, HD, 2 * HD), 2 * HD + 2 * HE, rank, w2, bias, s, out, starts, slots, heads, D, E, 16.0, D ** -0.5)
+    ms = (bk.timed_graph(all_layers, reps=1) if tokens_per_req == 1 else bk.timed(all_layers, n=5, warm=2)) / layers
+    nbytes = 2 * reqs * heads * D * E * 4 + T * (3 * HD + 2 * HE) * 4      # the state read and written; q, k, alpha, v, o
+    return {"kernel": "gla (decay + chain)", "requests": reqs, "tokens_per_request": tokens_per_req, "heads": heads, "dim": D,
+            "vdim": E, "us": round(ms * 1e3, 2), "tokens/s": round(T / ms * 1e3, 1), "GB/s": round(nbytes / ms / 1e6, 1),
+            "fp32 TFLOP/s": round(4.0 * D * E * heads * T / ms / 1e9, 2)}
+
+
+def streams_norm(tokens: int, S: int, H: int) -> dict:
+    """The launch between two sublayers of a model with S residual streams, and the adding norm of a model with one."""
+    import torch
+    import bench_kernels as bk
+    from quanta_b200 import kernels as k
+    dev = bk.DEV
+    n = max(1, int(1.5e9 // (tokens * (2 * S + 1) * H * 4)))
+    xs = [torch.randn(tokens, S, H, device=dev) for _ in range(n)]
+    hs = [torch.randn(tokens, H, device=dev) for _ in range(n)]
+    y = torch.randn(tokens, H, device=dev)
+    mix, out_w, read_w = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(S, device=dev)
+    w = torch.ones(H, device=dev)
+    out = torch.empty(tokens, H, device=dev, dtype=torch.bfloat16)
+
+    def many_streams():
+        for x in xs:
+            k.streams_mix_rmsnorm(x, y, mix, out_w, 0.7, read_w, w, 1e-5, out)
+
+    def one_stream():
+        for h in hs:
+            k.add_rmsnorm(h, y, w, 1e-5, out)
+    a = bk.timed_graph(many_streams, reps=1) / n
+    b = bk.timed_graph(one_stream, reps=1) / n
+    bytes_a, bytes_b = tokens * ((2 * S + 1) * H * 4 + H * 2), tokens * (3 * H * 4 + H * 2)
+    return {"kernel": "streams_mix_rmsnorm", "tokens": tokens, "streams": S, "width": H, "us": round(a * 1e3, 2),
+            "GB/s": round(bytes_a / a / 1e6, 1), "add_rmsnorm_us": round(b * 1e3, 2), "add_rmsnorm_GB/s": round(bytes_b / b / 1e6, 1)}
+
+
+def run_tirizen(args) -> dict:
+    import bench
+    from quanta_b200.config import MiniMaxM3Config, TirizenConfig
+    pk, pk_src = bench.peaks()
+    clocks = bench.ClockSampler()
+    clocks.start()
+    models = {}
+    for name, s in TIRIZEN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        t0 = time.time()
+        t = _model_numbers(TirizenConfig.from_dict(tirizen_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        m = _model_numbers(MiniMaxM3Config.from_dict(minimax_raw(s)), args.prompt_len, args.batch, args.steps, args.warmup)
+        models[name] = {"sizes": s, "tirizen": t, "minimax_m3": m}
+        print(f"[bench] {name}: tirizen {t}\n[bench] {name}: minimax_m3 {m} ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
+    s = TIRIZEN_SIZES["w2048"]
+    T, B, hbm = args.prompt_len, args.batch, pk["hbm_gbs"] * 1e9
+    gp, gd = gla(T, 1, s["gla_heads"], s["gla_dim"], s["gla_dim"]), gla(1, B, s["gla_heads"], s["gla_dim"], s["gla_dim"])
+    dp, dd = delta_rule(T, 1, s["gla_heads"], s["gla_dim"]), delta_rule(1, B, s["gla_heads"], s["gla_dim"])
+    sn_p, sn_d = streams_norm(T, s["streams"], s["width"]), streams_norm(B, s["streams"], s["width"])
+    for r in (gp, gd, dp, dd, sn_p, sn_d):
+        r["frac_of_copy_bandwidth"] = round(r["GB/s"] * 1e9 / hbm, 4)
+    for r in (sn_p, sn_d):
+        r["add_rmsnorm_frac_of_copy_bandwidth"] = round(r["add_rmsnorm_GB/s"] * 1e9 / hbm, 4)
+    kernels_alone = {"recurrence_prompt": {"tirizen": gp, "guravik": dp}, "recurrence_single_tokens": {"tirizen": gd, "guravik": dd},
+                     "between_sublayers_prompt": sn_p, "between_sublayers_single_tokens": sn_d}
+    for k_, v in kernels_alone.items():
+        print(f"[bench] {k_}: {v}", file=sys.stderr, flush=True)
+    first = next(iter(models.values()))["tirizen"] if models else {}
+    return {"metric": f"Tirizen decode tokens/s (batch {args.batch}, {args.prompt_len}-token prompts) beside MiniMax-M3 at equal sizes",
+            "value": first.get("decode_tok_s"), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": first.get("decode_ms"), "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (seeded uniform token ids, seeded random weights)", "design": "tirizen", "models": models,
+            "kernels": kernels_alone, "peaks": {**pk, "source": pk_src}, "clocks": clocks.stop(),
+            "gpu_launches": first.get("launches_per_decode_step", 0) * args.steps, "impl": "ours"}
+
+
 def run(args) -> dict:
+    if getattr(args, "design", "guravik") == "tirizen":
+        return run_tirizen(args)
     import torch
     import bench
     import bench_kernels as bk
@@ -229,7 +351,7 @@ if __name__ == "__main__":
     # one kernel alone, one JSON line:  python bench_designs.py latent_prefill --tokens 1024
     import argparse
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["latent_prefill", "latent_decode", "delta_rule"])
+    ap.add_argument("kernel", choices=["latent_prefill", "latent_decode", "delta_rule", "gla", "streams_norm"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--heads", type=int, default=16)
@@ -241,5 +363,9 @@ if __name__ == "__main__":
         print(json.dumps(latent_prefill(a.tokens, a.heads, a.latent, a.rot)))
     elif a.kernel == "latent_decode":
         print(json.dumps(latent_decode(a.batch, a.tokens, a.heads, a.latent, a.rot)))
+    elif a.kernel == "gla":
+        print(json.dumps(gla(a.tokens, a.batch, a.heads, a.dim, a.dim)))
+    elif a.kernel == "streams_norm":
+        print(json.dumps(streams_norm(a.tokens, 3, 2048)))
     else:
         print(json.dumps(delta_rule(a.tokens, a.batch, a.heads, a.dim)))

@@ -263,8 +263,10 @@ extern "C" int qb_silu_mul(const void* gu, void* out, int dtype, int n_rows, int
 // ---------------------------------------------------------------------------------------------
 constexpr int QB_MAX_STREAMS = 16;
 
-template <typename D, typename O>
-__global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, int S, const D* __restrict__ delta, int K,
+// SS: the number of streams when it is known at compile time (1 to 4: the streams' values stay in registers and rows
+// whose width is a multiple of 8 move in 16- and 32-byte pieces), 0: any number up to QB_MAX_STREAMS.
+template <typename D, typename O, int SS>
+__global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, int S_rt, const D* __restrict__ delta, int K,
                                            const float* __restrict__ mix, const float* __restrict__ out_w, float mult,
                                            const float* __restrict__ read_w, const float* __restrict__ w,
                                            O* __restrict__ out, const int* __restrict__ rows, int n_rows, int H,
@@ -272,6 +274,7 @@ __global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, int S, const D
   extern __shared__ float sm_u[];          // H floats (u) + 32 scratch
   float* scratch = sm_u + H;
   __shared__ float s_mix[QB_MAX_STREAMS * QB_MAX_STREAMS], s_out[QB_MAX_STREAMS], s_read[QB_MAX_STREAMS];
+  const int S = SS > 0 ? SS : S_rt;
   const int r = blockIdx.x;
   if (r >= n_rows) return;
   const int tok = rows ? rows[r] : r;
@@ -284,32 +287,88 @@ __global__ void streams_mix_rmsnorm_kernel(float* __restrict__ x, int S, const D
   float* xrow = x + (size_t)tok * S * H;
   const D* drow = delta ? delta + (size_t)tok * K * H : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float xs[QB_MAX_STREAMS];
-    for (int s = 0; s < S; ++s) xs[s] = xrow[(size_t)s * H + i];
-    float u = 0.f;
-    if (drow != nullptr) {
-      float y = 0.f;
-      for (int k = 0; k < K; ++k) y += qb_to_float<D>(drow[(size_t)k * H + i]);
-      for (int t = 0; t < S; ++t) {
-        float v = 0.f;
-        for (int s = 0; s < S; ++s) v = fmaf(s_mix[s * S + t], xs[s], v);
-        v = fmaf(s_out[t], y, v);
-        if (store) xrow[(size_t)t * H + i] = v;
-        u = fmaf(s_read[t], v, u);
+  if (SS > 0 && H % 8 == 0) {
+    constexpr int SC = SS > 0 ? SS : 1;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float xs[SC][8], u[8];
+#pragma unroll
+      for (int s = 0; s < SC; ++s) QbVec8<float>::load(xrow + (size_t)s * H + i, xs[s]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) u[e] = 0.f;
+      if (drow != nullptr) {
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = 0.f;
+        for (int k = 0; k < K; ++k) {
+          float dv[8];
+          QbVec8<D>::load(drow + (size_t)k * H + i, dv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] += dv[e];
+        }
+#pragma unroll
+        for (int t = 0; t < SC; ++t) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < SC; ++s) acc = fmaf(s_mix[s * SC + t], xs[s][e], acc);
+            v[e] = fmaf(s_out[t], y[e], acc);
+            u[e] = fmaf(s_read[t], v[e], u[e]);
+          }
+          if (store) QbVec8<float>::store(xrow + (size_t)t * H + i, v);
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < SC; ++t)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) u[e] = fmaf(s_read[t], xs[t][e], u[e]);
       }
-    } else {
-      for (int t = 0; t < S; ++t) u = fmaf(s_read[t], xs[t], u);
+      QbVec8<float>::store(sm_u + i, u);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += u[e] * u[e];
     }
-    sm_u[i] = u;
-    ss += u * u;
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float xs[QB_MAX_STREAMS];
+      for (int s = 0; s < S; ++s) xs[s] = xrow[(size_t)s * H + i];
+      float u = 0.f;
+      if (drow != nullptr) {
+        float y = 0.f;
+        for (int k = 0; k < K; ++k) y += qb_to_float<D>(drow[(size_t)k * H + i]);
+        for (int t = 0; t < S; ++t) {
+          float v = 0.f;
+          for (int s = 0; s < S; ++s) v = fmaf(s_mix[s * S + t], xs[s], v);
+          v = fmaf(s_out[t], y, v);
+          if (store) xrow[(size_t)t * H + i] = v;
+          u = fmaf(s_read[t], v, u);
+        }
+      } else {
+        for (int t = 0; t < S; ++t) u = fmaf(s_read[t], xs[t], u);
+      }
+      sm_u[i] = u;
+      ss += u * u;
+    }
   }
   if (out == nullptr) return;
   const float total = qb_block_sum(ss, scratch);
   const float r_inv = w != nullptr ? rsqrtf(total / (float)H + eps) : 1.f;
   O* orow = out + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    orow[i] = qb_from_float<O>(w != nullptr ? w[i] * (sm_u[i] * r_inv) : sm_u[i]);
+  if (H % 8 == 0) {
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float u[8], wv[8];
+      QbVec8<float>::load(sm_u + i, u);
+      if (w != nullptr) {
+        QbVec8<float>::load(w + i, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) u[e] = wv[e] * (u[e] * r_inv);
+      }
+      QbVec8<O>::store(orow + i, u);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      orow[i] = qb_from_float<O>(w != nullptr ? w[i] * (sm_u[i] * r_inv) : sm_u[i]);
+  }
 }
 
 extern "C" int qb_streams_mix_rmsnorm(float* x, int S, const void* delta, int delta_dtype, int K, const float* mix,
@@ -321,16 +380,25 @@ extern "C" int qb_streams_mix_rmsnorm(float* x, int S, const void* delta, int de
   if (delta != nullptr && (mix == nullptr || out_w == nullptr || K < 1)) return QB_ERR_BAD_ARG;
   const size_t smem = (size_t)(H + 32) * sizeof(float);
   if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
-  const int threads = H >= 2048 ? 512 : 256;
+  const int threads = H >= 4096 ? 512 : 256;
+#define QB_STREAMS(SS_)                                                                                          \
+  do {                                                                                                           \
+    auto kern = streams_mix_rmsnorm_kernel<D, O, SS_>;                                                           \
+    if (smem > 48 * 1024) {                                                                                      \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+      if (e != cudaSuccess) return (int)e;                                                                       \
+    }                                                                                                            \
+    kern<<<n_rows, threads, smem, stream>>>(x, S, (const D*)delta, K, mix, out_w, mult, read_w, w, (O*)out, rows, \
+                                            n_rows, H, eps, store);                                              \
+  } while (0)
   QB_DISPATCH_DTYPE(delta_dtype, D, QB_DISPATCH_DTYPE(out_dtype, O, {
-    auto kern = streams_mix_rmsnorm_kernel<D, O>;
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    kern<<<n_rows, threads, smem, stream>>>(x, S, (const D*)delta, K, mix, out_w, mult, read_w, w, (O*)out, rows,
-                                            n_rows, H, eps, store);
+    if (S == 1) QB_STREAMS(1);
+    else if (S == 2) QB_STREAMS(2);
+    else if (S == 3) QB_STREAMS(3);
+    else if (S == 4) QB_STREAMS(4);
+    else QB_STREAMS(0);
   }));
+#undef QB_STREAMS
   QB_LAUNCH_CHECK();
   return 0;
 }
