@@ -659,12 +659,13 @@ GLA_MAX_DIM = 256
 
 
 def gla(proj, offsets, inner_off: int, rank: int, w2, bias, state, out, req_start, req_slot, n_heads: int, dim: int,
-        vdim: int, tau: float, q_scale: float) -> None:
+        vdim: int, tau: float, q_scale: float, segments: bool | None = None) -> None:
     """Gated linear attention ``S <- diag(alpha) S + k v^T``, ``o = q_scale * S^T q`` per (request, head) over the
     step's tokens, from and into ``state`` ``[slots, heads, dim, vdim]`` float32.  ``proj`` float32 ``[T, P]`` holds
     q, k (heads x dim) and v (heads x vdim) at the column ``offsets`` (q, k, v) and the ``rank`` inner values of
     the decay at ``inner_off``; ``alpha = sigmoid(w2 inner + bias) ^ (1 / tau)`` with ``w2`` ``[heads*dim, rank]``
-    and ``bias`` float32; ``out`` float32 ``[T, heads, vdim]``."""
+    and ``bias`` float32; ``out`` float32 ``[T, heads, vdim]``.  ``segments`` False keeps a step with long
+    portions on the one chain in time (else such steps run as segments in three passes)."""
     for t, n in ((proj, "proj"), (bias, "bias"), (state, "state"), (out, "out")):
         _want(t, torch.float32, n)
     T = proj.shape[0]
@@ -676,10 +677,16 @@ def gla(proj, offsets, inner_off: int, rank: int, w2, bias, state, out, req_star
         raise ValueError("gla: shape mismatch")
     R = req_slot.numel()
     scratch = torch.empty(T * HD, dtype=torch.float32, device=proj.device)      # alpha of every (token, channel)
+    # steps with long portions run as segments in three passes (see the kernel file); they need room for a state
+    # per segment
+    fn = lib().qb_gla_segment_scratch
+    fn.restype = ctypes.c_longlong
+    n_seg_floats = int(fn(R, T, n_heads, dim, vdim)) if segments is not False else 0
+    seg_scratch = torch.empty(n_seg_floats, dtype=torch.float32, device=proj.device) if n_seg_floats else None
     _check(lib().qb_gla(ctypes.c_void_p(proj.data_ptr()), int(proj.stride(0)), q_off, k_off, v_off, int(inner_off),
-                        int(rank), _p(w2), _code(w2), _p(bias), _p(state), _p(out), _p(scratch), _p(req_start),
-                        _p(req_slot), R, T, n_heads, dim, vdim, ctypes.c_float(tau), ctypes.c_float(q_scale),
-                        _stream()), "gla", 2)
+                        int(rank), _p(w2), _code(w2), _p(bias), _p(state), _p(out), _p(scratch), _p(seg_scratch),
+                        _p(req_start), _p(req_slot), R, T, n_heads, dim, vdim, ctypes.c_float(tau),
+                        ctypes.c_float(q_scale), _stream()), "gla", 5 if n_seg_floats else 2)
 
 
 def tanh_cols(x, off: int, n: int, out) -> None:

@@ -404,6 +404,62 @@ def test_gated_linear_recurrence_alone(dim, vdim, heads, rank):
     assert float(state[1].min()) == 5.0
 
 
+@pytest.mark.parametrize("dim,vdim,heads", [(64, 64, 3), (24, 40, 2), (136, 16, 1)])
+def test_long_portions_run_as_segments(dim, vdim, heads):
+    """A step with long portions cuts every request into segments that run side by side (each from a zero state,
+    then joined in order, then once more from their true start states): the same numbers, to rounding, as the one
+    chain in time and as the plain loop; requests of 700, 1, 65 and 64 tokens in one call (segments that end on,
+    before and after a border), states that are not zero when the call begins."""
+    from quanta_b200 import kernels
+    dev, rank = "cuda:0", 6
+    g = torch.Generator().manual_seed(dim)
+    HD, HE = heads * dim, heads * vdim
+    lengths = [[5, 1, 3, 2], [700, 1, 65, 64]]
+    total = [sum(x) for x in zip(*lengths)]
+    n_all = sum(total)
+    proj = torch.randn(n_all, 2 * HD + HE + rank, generator=g)
+    w2 = torch.randn(HD, rank, generator=g)
+    bias = 3.0 + 1.5 * torch.randn(HD, generator=g)
+    tau, q_scale = 8.0, dim ** -0.5
+    rows_of, at = [], 0
+    for r in range(4):
+        rows_of.append(list(range(at, at + total[r])))
+        at += total[r]
+    results = {}
+    for segments in (None, False):
+        state = torch.full((6, heads, dim, vdim), 5.0, device=dev)
+        slots = [2, 0, 5, 3]
+        for s in slots:
+            state[s].zero_()
+        got = torch.zeros(n_all, heads, vdim)
+        done = [0] * 4
+        for call in lengths:
+            idx = [i for r in range(4) for i in rows_of[r][done[r]: done[r] + call[r]]]
+            starts, sl = _ctx_arrays(call, slots, dev)
+            out = torch.empty(len(idx), heads, vdim, device=dev)
+            before = kernels.LAUNCHES
+            kernels.gla(proj[idx].to(dev).contiguous(), (0, HD, 2 * HD), 2 * HD + HE, rank, w2.to(dev), bias.to(dev), state, out,
+                        starts, sl, heads, dim, vdim, tau, q_scale, segments=segments)
+            assert kernels.LAUNCHES - before == (5 if segments is None and len(idx) >= 512 else 2)
+            got[idx] = out.cpu()
+            for r in range(4):
+                done[r] += call[r]
+        results[segments] = (got, state.cpu())
+        assert float(state[1].min()) == 5.0 and float(state[4].min()) == 5.0
+    (a, sa), (b, sb) = results[None], results[False]
+    assert torch.allclose(a, b, atol=2e-5 * float(b.abs().max()), rtol=1e-4)
+    assert torch.allclose(sa, sb, atol=2e-5 * float(sb.abs().max()), rtol=1e-4)
+    for r in range(4):
+        rows = rows_of[r]
+        q = proj[rows, :HD].view(-1, heads, dim) * q_scale
+        k = proj[rows, HD: 2 * HD].view(-1, heads, dim)
+        v = proj[rows, 2 * HD: 2 * HD + HE].view(-1, heads, vdim)
+        z = proj[rows, 2 * HD + HE: 2 * HD + HE + rank] @ w2.T + bias
+        alpha = torch.sigmoid(z.double()).pow(1.0 / tau).float().view(-1, heads, dim)
+        want, _ = P.gated_linear_recurrence(q, k, v, alpha)
+        assert torch.allclose(a[rows], want, atol=3e-5 * float(want.abs().max()), rtol=1e-4), r
+
+
 def test_a_far_token_stays_in_the_recurrent_state():
     """With decays at 1 - 2e-4 a token 600 steps back still weighs 0.89: its value comes out when the query meets
     its key, through a state that crossed 40 calls of unequal size."""
