@@ -29,12 +29,64 @@
 constexpr int GLA_LANES = 4;          // lanes that share a column
 constexpr int GLA_MAX_THREADS = 256;  // a block: 64 groups of four lanes, each group one or two columns
 
-// alpha[t, c] for every token and channel c < C (= heads * D): one thread a (token, channel); the inner
-// product over the rank L is one sequential float32 sum, the same whatever else the step holds.
+// alpha[t, c] for every token and channel c < C (= heads * D).  A block takes 128 channels and GLA_DECAY_TOKENS
+// tokens: the channels' rows of W2 (transposed) and the tokens' L inner values (transposed) lie in shared memory,
+// a thread owns one channel and walks the rank once for all the block's tokens.  The inner product over the rank
+// L is one sequential float32 sum in index order, the same whatever else the step holds.
+constexpr int GLA_DECAY_TOKENS = 16, GLA_DECAY_CHANNELS = 128;
+
 template <typename W>
-__global__ void gla_decay_kernel(const float* __restrict__ proj, int proj_stride, int inner_off, int L,
-                                 const W* __restrict__ w2, const float* __restrict__ bias, float* __restrict__ alpha,
-                                 int T, int C, float inv_tau) {
+__global__ void __launch_bounds__(GLA_DECAY_CHANNELS)
+gla_decay_kernel(const float* __restrict__ proj, int proj_stride, int inner_off, int L,
+                 const W* __restrict__ w2, const float* __restrict__ bias, float* __restrict__ alpha,
+                 int T, int C, float inv_tau) {
+  extern __shared__ __align__(16) float s_dec[];
+  float* s_w = s_dec;                                   // [L][128]
+  float* s_in = s_dec + (size_t)L * GLA_DECAY_CHANNELS;   // [L][GLA_DECAY_TOKENS]
+  const int c0 = blockIdx.x * GLA_DECAY_CHANNELS, t0 = blockIdx.y * GLA_DECAY_TOKENS;
+  const int nt = min(GLA_DECAY_TOKENS, T - t0);
+  for (int idx = threadIdx.x; idx < GLA_DECAY_CHANNELS * L; idx += blockDim.x) {
+    const int c = idx / L, i = idx % L;                 // consecutive threads read consecutive elements of W2
+    s_w[i * GLA_DECAY_CHANNELS + c] = c0 + c < C ? qb_to_float<W>(w2[(size_t)(c0 + c) * L + i]) : 0.f;
+  }
+  for (int idx = threadIdx.x; idx < GLA_DECAY_TOKENS * L; idx += blockDim.x) {
+    const int tt = idx / L, i = idx % L;
+    s_in[i * GLA_DECAY_TOKENS + tt] = tt < nt ? proj[(size_t)(t0 + tt) * proj_stride + inner_off + i] : 0.f;
+  }
+  __syncthreads();
+  const int c = c0 + threadIdx.x;
+  float z[GLA_DECAY_TOKENS];
+#pragma unroll
+  for (int tt = 0; tt < GLA_DECAY_TOKENS; ++tt) z[tt] = 0.f;
+  for (int i = 0; i < L; ++i) {
+    const float w = s_w[i * GLA_DECAY_CHANNELS + threadIdx.x];
+#pragma unroll
+    for (int tt = 0; tt < GLA_DECAY_TOKENS; tt += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(s_in + i * GLA_DECAY_TOKENS + tt);
+      z[tt] = fmaf(w, x.x, z[tt]);
+      z[tt + 1] = fmaf(w, x.y, z[tt + 1]);
+      z[tt + 2] = fmaf(w, x.z, z[tt + 2]);
+      z[tt + 3] = fmaf(w, x.w, z[tt + 3]);
+    }
+  }
+  if (c >= C) return;
+  const float b = bias[c];
+#pragma unroll
+  for (int tt = 0; tt < GLA_DECAY_TOKENS; ++tt) {
+    if (tt < nt) {
+      const float zz = z[tt] + b;
+      const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
+      alpha[(size_t)(t0 + tt) * C + c] = expf(ls * inv_tau);
+    }
+  }
+}
+
+// The same for steps of few tokens: one thread a (token, channel), a block a token and 128 channels, so that the few
+// tokens' channels spread over many SMs; the same sum in the same order.
+template <typename W>
+__global__ void gla_decay_small_kernel(const float* __restrict__ proj, int proj_stride, int inner_off, int L,
+                                       const W* __restrict__ w2, const float* __restrict__ bias,
+                                       float* __restrict__ alpha, int T, int C, float inv_tau) {
   extern __shared__ float s_inner[];      // the token's L inner values
   const int t = blockIdx.y;
   const float* in = proj + (size_t)t * proj_stride + inner_off;
@@ -95,12 +147,25 @@ __global__ void gla_combine_kernel(float* __restrict__ state, float* __restrict_
   for (int idx = blockIdx.z * blockDim.x + threadIdx.x; idx < D * E; idx += gridDim.z * blockDim.x) {
     const int i = idx / E;
     float s = S[idx];
-    for (int c = 0; c < rs.y; ++c) {
-      const size_t sg = (size_t)(rs.x + c) * H + h;
-      float* L = seg_state + sg * D * E + idx;
-      const float l = *L, p = seg_decay[sg * D + i];
-      *L = s;                          // the state this segment starts from
-      s = fmaf(p, s, l);
+    // eight segments a turn: their loads are in flight together, then the short chain, then the stores
+    for (int c0 = 0; c0 < rs.y; c0 += 8) {
+      float l[8], p[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (c0 + u < rs.y) {
+          const size_t sg = (size_t)(rs.x + c0 + u) * H + h;
+          l[u] = __ldcg(seg_state + sg * D * E + idx);
+          p[u] = __ldcg(seg_decay + sg * D + i);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (c0 + u < rs.y) {
+          const size_t sg = (size_t)(rs.x + c0 + u) * H + h;
+          seg_state[sg * D * E + idx] = s;      // the state this segment starts from
+          s = fmaf(p[u], s, l[u]);
+        }
+      }
     }
     S[idx] = s;
   }
@@ -276,13 +341,24 @@ extern "C" int qb_gla(const float* proj, int proj_stride, int q_off, int k_off, 
                       float tau, float q_scale, cudaStream_t stream) {
   if (R <= 0 || T <= 0) return 0;
   if (D <= 0 || D > 256 || E <= 0 || E > 256 || H <= 0 || L <= 0 || tau <= 0.f) return QB_ERR_UNSUPPORTED;
-  if (L * sizeof(float) > 48 * 1024) return QB_ERR_UNSUPPORTED;
   const int C = H * D;
   {
-    dim3 grid((C + 127) / 128, T);
+    const size_t smem = (size_t)L * (GLA_DECAY_CHANNELS + GLA_DECAY_TOKENS) * sizeof(float);
+    if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
+    dim3 grid((C + GLA_DECAY_CHANNELS - 1) / GLA_DECAY_CHANNELS, (T + GLA_DECAY_TOKENS - 1) / GLA_DECAY_TOKENS);
     if (grid.y > 65535) return QB_ERR_UNSUPPORTED;
-    QB_DISPATCH_DTYPE(w2_dtype, W, gla_decay_kernel<W><<<grid, 128, L * sizeof(float), stream>>>(
-        proj, proj_stride, inner_off, L, (const W*)w2, bias, scratch, T, C, 1.f / tau));
+    if (T < 64) {
+      QB_DISPATCH_DTYPE(w2_dtype, W, gla_decay_small_kernel<W><<<dim3((C + 127) / 128, T), 128, L * sizeof(float), stream>>>(
+          proj, proj_stride, inner_off, L, (const W*)w2, bias, scratch, T, C, 1.f / tau));
+    } else QB_DISPATCH_DTYPE(w2_dtype, W, {
+      auto kern = gla_decay_kernel<W>;
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+      }
+      kern<<<grid, GLA_DECAY_CHANNELS, smem, stream>>>(proj, proj_stride, inner_off, L, (const W*)w2, bias, scratch, T, C,
+                                                       1.f / tau);
+    });
     QB_LAUNCH_CHECK();
   }
   const bool segmented = seg_scratch != nullptr && qb_gla_segment_scratch(R, T, H, D, E) > 0;
