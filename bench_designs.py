@@ -64,13 +64,13 @@ def tirizen_raw(s: dict) -> dict:
     layers = []
     for g in range(s["groups"]):
         attn = {"heads": s["attn_heads"], "kv_heads": max(1, s["attn_heads"] // 4), "dim": s["dim"], "vdim": s["dim"],
-                "scale": 1.0 / math.sqrt(s["dim"]), "q_temp": {"coef": 0.3, "every": 256}}
+                "scale": 1.0 / math.sqrt(s["dim"]), "q_temp": {"coef": 0.25, "every": 512}}
         layers += [{"type": "attention", "mixer": dict(attn), "mlp": moe},
-                   {"type": "gla", "mixer": {"heads": s["gla_heads"], "dim": s["gla_dim"], "vdim": s["gla_dim"], "tau": 16.0,
-                                             "decay_rank": 16}, "mlp": moe},
+                   {"type": "gla", "mixer": {"heads": s["gla_heads"], "dim": s["gla_dim"], "vdim": s["gla_dim"], "tau": 8.0,
+                                             "decay_rank": 32}, "mlp": moe},
                    {"type": "attention", "mixer": dict(attn, kv_from=3 * g), "mlp": moe}]
     return {"architecture": "Tirizen", "vocab": s["vocab"], "width": s["width"], "layers": layers, "streams": s["streams"],
-            "residual_mult": 0.7, "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "residual_mult": 0.8, "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-5},
             "max_positions": 8192}
 
 
