@@ -29,11 +29,12 @@
 constexpr int GLA_LANES = 4;          // lanes that share a column
 constexpr int GLA_MAX_THREADS = 256;  // a block: 64 groups of four lanes, each group one or two columns
 
-// alpha[t, c] for every token and channel c < C (= heads * D).  A block takes 128 channels and GLA_DECAY_TOKENS
-// tokens: the channels' rows of W2 (transposed) and the tokens' L inner values (transposed) lie in shared memory,
+// alpha[t, c] for every token and channel c < C (= heads * D).  A block takes 128 channels and GLA_DECAY_ROUNDS rounds
+// of GLA_DECAY_TOKENS tokens: the channels' rows of W2 (transposed) and the tokens' L inner values (transposed) lie in shared memory,
 // a thread owns one channel and walks the rank once for all the block's tokens.  The inner product over the rank
 // L is one sequential float32 sum in index order, the same whatever else the step holds.
-constexpr int GLA_DECAY_TOKENS = 16, GLA_DECAY_CHANNELS = 128;
+constexpr int GLA_DECAY_TOKENS = 16, GLA_DECAY_ROUNDS = 4, GLA_DECAY_CHANNELS = 128;
+constexpr int GLA_DECAY_WS = GLA_DECAY_CHANNELS + 1;      // floats between two rank rows of W2 in shared memory (no bank conflicts)
 
 template <typename W>
 __global__ void __launch_bounds__(GLA_DECAY_CHANNELS)
@@ -41,42 +42,49 @@ gla_decay_kernel(const float* __restrict__ proj, int proj_stride, int inner_off,
                  const W* __restrict__ w2, const float* __restrict__ bias, float* __restrict__ alpha,
                  int T, int C, float inv_tau) {
   extern __shared__ __align__(16) float s_dec[];
-  float* s_w = s_dec;                                   // [L][128]
-  float* s_in = s_dec + (size_t)L * GLA_DECAY_CHANNELS;   // [L][GLA_DECAY_TOKENS]
-  const int c0 = blockIdx.x * GLA_DECAY_CHANNELS, t0 = blockIdx.y * GLA_DECAY_TOKENS;
-  const int nt = min(GLA_DECAY_TOKENS, T - t0);
+  float* s_in = s_dec;                                        // [L][GLA_DECAY_TOKENS]
+  float* s_w = s_dec + (size_t)L * GLA_DECAY_TOKENS;          // [L][GLA_DECAY_WS]
+  const int c0 = blockIdx.x * GLA_DECAY_CHANNELS;
   for (int idx = threadIdx.x; idx < GLA_DECAY_CHANNELS * L; idx += blockDim.x) {
     const int c = idx / L, i = idx % L;                 // consecutive threads read consecutive elements of W2
-    s_w[i * GLA_DECAY_CHANNELS + c] = c0 + c < C ? qb_to_float<W>(w2[(size_t)(c0 + c) * L + i]) : 0.f;
+    s_w[i * GLA_DECAY_WS + c] = c0 + c < C ? qb_to_float<W>(w2[(size_t)(c0 + c) * L + i]) : 0.f;
   }
-  for (int idx = threadIdx.x; idx < GLA_DECAY_TOKENS * L; idx += blockDim.x) {
-    const int tt = idx / L, i = idx % L;
-    s_in[i * GLA_DECAY_TOKENS + tt] = tt < nt ? proj[(size_t)(t0 + tt) * proj_stride + inner_off + i] : 0.f;
-  }
-  __syncthreads();
   const int c = c0 + threadIdx.x;
-  float z[GLA_DECAY_TOKENS];
-#pragma unroll
-  for (int tt = 0; tt < GLA_DECAY_TOKENS; ++tt) z[tt] = 0.f;
-  for (int i = 0; i < L; ++i) {
-    const float w = s_w[i * GLA_DECAY_CHANNELS + threadIdx.x];
-#pragma unroll
-    for (int tt = 0; tt < GLA_DECAY_TOKENS; tt += 4) {
-      const float4 x = *reinterpret_cast<const float4*>(s_in + i * GLA_DECAY_TOKENS + tt);
-      z[tt] = fmaf(w, x.x, z[tt]);
-      z[tt + 1] = fmaf(w, x.y, z[tt + 1]);
-      z[tt + 2] = fmaf(w, x.z, z[tt + 2]);
-      z[tt + 3] = fmaf(w, x.w, z[tt + 3]);
+  const float b = c < C ? bias[c] : 0.f;
+  // the block's tokens in rounds of GLA_DECAY_TOKENS: the rows of W2 are staged once for all of them
+  for (int round = 0; round < GLA_DECAY_ROUNDS; ++round) {
+    const int t0 = (blockIdx.y * GLA_DECAY_ROUNDS + round) * GLA_DECAY_TOKENS;
+    if (t0 >= T) break;
+    const int nt = min(GLA_DECAY_TOKENS, T - t0);
+    __syncthreads();                                    // the round before is done with s_in
+    for (int idx = threadIdx.x; idx < GLA_DECAY_TOKENS * L; idx += blockDim.x) {
+      const int i = idx / GLA_DECAY_TOKENS, tt = idx % GLA_DECAY_TOKENS;
+      s_in[i * GLA_DECAY_TOKENS + tt] = tt < nt ? proj[(size_t)(t0 + tt) * proj_stride + inner_off + i] : 0.f;
     }
-  }
-  if (c >= C) return;
-  const float b = bias[c];
+    __syncthreads();
+    float z[GLA_DECAY_TOKENS];
 #pragma unroll
-  for (int tt = 0; tt < GLA_DECAY_TOKENS; ++tt) {
-    if (tt < nt) {
-      const float zz = z[tt] + b;
-      const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
-      alpha[(size_t)(t0 + tt) * C + c] = expf(ls * inv_tau);
+    for (int tt = 0; tt < GLA_DECAY_TOKENS; ++tt) z[tt] = 0.f;
+    for (int i = 0; i < L; ++i) {
+      const float w = s_w[i * GLA_DECAY_WS + threadIdx.x];
+#pragma unroll
+      for (int tt = 0; tt < GLA_DECAY_TOKENS; tt += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(s_in + i * GLA_DECAY_TOKENS + tt);
+        z[tt] = fmaf(w, x.x, z[tt]);
+        z[tt + 1] = fmaf(w, x.y, z[tt + 1]);
+        z[tt + 2] = fmaf(w, x.z, z[tt + 2]);
+        z[tt + 3] = fmaf(w, x.w, z[tt + 3]);
+      }
+    }
+    if (c < C) {
+#pragma unroll
+      for (int tt = 0; tt < GLA_DECAY_TOKENS; ++tt) {
+        if (tt < nt) {
+          const float zz = z[tt] + b;
+          const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));
+          alpha[(size_t)(t0 + tt) * C + c] = expf(ls * inv_tau);
+        }
+      }
     }
   }
 }
@@ -343,9 +351,10 @@ extern "C" int qb_gla(const float* proj, int proj_stride, int q_off, int k_off, 
   if (D <= 0 || D > 256 || E <= 0 || E > 256 || H <= 0 || L <= 0 || tau <= 0.f) return QB_ERR_UNSUPPORTED;
   const int C = H * D;
   {
-    const size_t smem = (size_t)L * (GLA_DECAY_CHANNELS + GLA_DECAY_TOKENS) * sizeof(float);
+    const size_t smem = (size_t)L * (GLA_DECAY_WS + GLA_DECAY_TOKENS) * sizeof(float);
     if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
-    dim3 grid((C + GLA_DECAY_CHANNELS - 1) / GLA_DECAY_CHANNELS, (T + GLA_DECAY_TOKENS - 1) / GLA_DECAY_TOKENS);
+    const int per_block = GLA_DECAY_TOKENS * GLA_DECAY_ROUNDS;
+    dim3 grid((C + GLA_DECAY_CHANNELS - 1) / GLA_DECAY_CHANNELS, (T + per_block - 1) / per_block);
     if (grid.y > 65535) return QB_ERR_UNSUPPORTED;
     if (T < 64) {
       QB_DISPATCH_DTYPE(w2_dtype, W, gla_decay_small_kernel<W><<<dim3((C + 127) / 128, T), 128, L * sizeof(float), stream>>>(

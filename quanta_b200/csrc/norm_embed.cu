@@ -432,21 +432,49 @@ template <typename O>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate,
                                       int gate_stride, const float* __restrict__ gain, O* __restrict__ out,
                                       int T, int H, int D, float eps, int gain_shared, int gate_kind) {
+  constexpr int MAXR = 8;          // elements a lane keeps in registers: heads of up to 256 are read once
   const int lane = threadIdx.x & 31;
   const long wid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= (long)T * H) return;
   const int t = (int)(wid / H), h = (int)(wid % H);
   const float* row = o + ((size_t)t * H + h) * D;
+  const float* g = gate + (size_t)t * gate_stride + (size_t)h * D;
+  const float* gn = gain + (gain_shared ? 0 : h * D);
+  O* orow = out + ((size_t)t * H + h) * D;
+  if (D <= 32 * MAXR) {
+    // everything the lane needs is asked for at once, before the sum across lanes
+    float rv[MAXR], gv[MAXR], nv[MAXR];
+#pragma unroll
+    for (int u = 0; u < MAXR; ++u) {
+      const int i = lane + 32 * u;
+      const bool in = i < D;
+      rv[u] = in ? row[i] : 0.f;
+      gv[u] = in ? g[i] : 0.f;
+      nv[u] = in ? gn[i] : 0.f;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < MAXR; ++u) ss += rv[u] * rv[u];
+    ss = qb_warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int u = 0; u < MAXR; ++u) {
+      const int i = lane + 32 * u;
+      if (i < D) {
+        const float sg = 1.f / (1.f + expf(-gv[u]));
+        orow[i] = qb_from_float<O>(rv[u] * inv * nv[u] * (gate_kind == 1 ? gv[u] * sg : sg));
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = lane; i < D; i += 32) ss += row[i] * row[i];
   ss = qb_warp_sum(ss);
   const float inv = 1.f / sqrtf(ss / (float)D + eps);
-  const float* g = gate + (size_t)t * gate_stride + (size_t)h * D;
-  const float* gn = gain + (gain_shared ? 0 : h * D);
   for (int i = lane; i < D; i += 32) {
     const float sg = 1.f / (1.f + expf(-g[i]));
     const float a = gate_kind == 1 ? g[i] * sg : sg;
-    out[((size_t)t * H + h) * D + i] = qb_from_float<O>(row[i] * inv * gn[i] * a);
+    orow[i] = qb_from_float<O>(row[i] * inv * gn[i] * a);
   }
 }
 
@@ -469,7 +497,22 @@ extern "C" int qb_head_norm_gate(const float* o, const float* gate, int gate_str
 // ---------------------------------------------------------------------------------------------
 template <typename A>
 __global__ void head_sigmoid_gate_kernel(A* __restrict__ x, const A* __restrict__ gate, int gate_stride, int T,
-                                         int H, int D) {
+                                         int H, int D, int vec) {
+  if (vec) {        // D a multiple of 8: eight elements of one head a thread, 16-byte moves
+    const size_t n8 = (size_t)T * H * D / 8;
+    const int d8 = D / 8;
+    for (size_t c = blockIdx.x * (size_t)blockDim.x + threadIdx.x; c < n8; c += (size_t)gridDim.x * blockDim.x) {
+      const size_t th = c / d8, t = th / H, h = th % H;
+      const float g = qb_to_float<A>(gate[t * gate_stride + h]);
+      const float sg = 1.f / (1.f + expf(-g));
+      float v[8];
+      QbVec8<A>::load(x + c * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] *= sg;
+      QbVec8<A>::store(x + c * 8, v);
+    }
+    return;
+  }
   const size_t n = (size_t)T * H * D;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t th = i / D, t = th / H, h = th % H;
@@ -481,10 +524,11 @@ __global__ void head_sigmoid_gate_kernel(A* __restrict__ x, const A* __restrict_
 extern "C" int qb_head_sigmoid_gate(void* x, const void* gate, int gate_stride, int dtype, int T, int H, int D,
                                     cudaStream_t stream) {
   if (T <= 0) return 0;
-  const size_t n = (size_t)T * H * D;
+  const int vec = (D % 8 == 0 && ((uintptr_t)x & 31) == 0) ? 1 : 0;
+  const size_t n = (size_t)T * H * D / (vec ? 8 : 1);
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   QB_DISPATCH_DTYPE(dtype, A, head_sigmoid_gate_kernel<A><<<blocks, 256, 0, stream>>>((A*)x, (const A*)gate,
-                                                                                      gate_stride, T, H, D));
+                                                                                      gate_stride, T, H, D, vec));
   QB_LAUNCH_CHECK();
   return 0;
 }
