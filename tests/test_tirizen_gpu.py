@@ -210,6 +210,38 @@ def test_cuttings_agree_with_plain(models, name, dtype):
         assert eng.manager.stats()["live_requests"] == 0
 
 
+ORDERS = {
+    # no layer keeps keys and values (the cache manager has no page group), none has a state, one layer only,
+    # two sources of shared keys and values read in turn, a shared source behind recurrent layers at the very end
+    "recurrence_only": [_gla(2, 16, 16, mlp=_dense(32)), _gla(1, 32, 8)],
+    "attention_only": [_attn(4, 2, 16, 16, mlp=_moe(4, 2, 16)), _attn(4, 2, 16, 16, kv_from=0)],
+    "one_layer": [_gla(2, 16, 24, mlp=_moe(3, 1, 8))],
+    "two_sources": [_attn(2, 1, 16, 16), _attn(4, 4, 8, 8), _attn(2, 1, 16, 16, kv_from=0), _attn(4, 4, 8, 8, kv_from=1),
+                    _attn(2, 1, 16, 16, kv_from=0)],
+    "shared_at_the_end": [_attn(2, 1, 32, 32), _gla(2, 8, 8), _gla(2, 8, 8, mlp=_dense(16)), _attn(2, 1, 32, 32, kv_from=0),
+                          _attn(2, 1, 32, 32, kv_from=0, mlp=_dense(8))],
+}
+
+
+@pytest.mark.parametrize("order", list(ORDERS))
+def test_other_orders_of_layers(tmp_path_factory, order):
+    cfg = _config(67, 40, ORDERS[order], streams=2 if order != "one_layer" else 0, mult=0.8, scale=2.0)
+    folder, weights, cfg = _folder(tmp_path_factory, "A", cfg=cfg, seed=3)
+    reqs = _requests(cfg["vocab"], [1, 40, 90], seed=1)
+    want, margins = _want(weights, cfg, reqs)
+    steps = H.cut_mixed(reqs, max_live=3, seed=5, portion_sizes=(2, 3, 5, 8, 17))
+    for dtype in ("float32", "bfloat16"):
+        eng = _engine(folder, dtype, steps, slots=3)
+        if dtype == "bfloat16":
+            got, following = _replay_following_the_routing(eng, steps, weights, cfg, reqs)
+            worst, where = _worst(got, following)
+        else:
+            got = H.replay(eng, steps)
+            worst, where = _worst(got, want, margins, NEAR_TIE[dtype])
+        assert worst < TOL[dtype], (order, dtype, worst, where)
+        eng.manager.check_invariants()
+
+
 def test_residual_stream_after_every_layer(models):
     """The sum of the streams after each layer (the model's own trace) against the plain implementation's."""
     from quanta_b200.engine.step import StepEntry
